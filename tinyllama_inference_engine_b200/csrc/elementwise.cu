@@ -187,17 +187,22 @@ __global__ void __launch_bounds__(kRowWarps * 32) add_rmsnorm_rows_kernel(float*
   }
 }
 
-// out[t, i..i+3] = silu(gate) * up for four neighbours at a time (inter % 4 == 0)
+// the gate's activation: 0 silu, 1 gelu in its tanh form
+__device__ __forceinline__ float gate_act(float g, int kind) {
+  if (kind == 1) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.0f + expf(-g));
+}
+
+// out[t, i..i+3] = act(gate) * up for four neighbours at a time (inter % 4 == 0)
 template <typename T>
-__global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total4) {
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total4, int kind) {
   const int per_row = inter / 4;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (size_t)gridDim.x * blockDim.x) {
     const size_t row = i / per_row;
     const int col = (int)(i - row * per_row) * 4;
     const float4 g = Vec4<T>::load(gate_up + row * 2 * inter + col);
     const float4 u = Vec4<T>::load(gate_up + row * 2 * inter + inter + col);
-    Vec4<T>::store(out + row * inter + col, make_float4((g.x / (1.0f + expf(-g.x))) * u.x, (g.y / (1.0f + expf(-g.y))) * u.y,
-                                                        (g.z / (1.0f + expf(-g.z))) * u.z, (g.w / (1.0f + expf(-g.w))) * u.w));
+    Vec4<T>::store(out + row * inter + col, make_float4(gate_act(g.x, kind) * u.x, gate_act(g.y, kind) * u.y, gate_act(g.z, kind) * u.z, gate_act(g.w, kind) * u.w));
   }
 }
 
@@ -208,15 +213,15 @@ __global__ void add_kernel(float* __restrict__ residual, const T* __restrict__ d
     residual[i] += to_float(delta[i]);
 }
 
-// out[t, i] = silu(gate_up[t, i]) * gate_up[t, inter + i]
+// out[t, i] = act(gate_up[t, i]) * gate_up[t, inter + i]
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total, int kind) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t row = i / inter;
     const int col = (int)(i - row * inter);
     const float g = to_float(gate_up[row * 2 * inter + col]);
     const float u = to_float(gate_up[row * 2 * inter + inter + col]);
-    out[i] = from_float<T>((g / (1.0f + expf(-g))) * u);
+    out[i] = from_float<T>(gate_act(g, kind) * u);
   }
 }
 
@@ -346,7 +351,9 @@ TLIE_EXPORT int tlie_add(int dtype, float* residual, const void* delta, long lon
   return (int)cudaGetLastError();
 }
 
-TLIE_EXPORT int tlie_silu_mul(int dtype, const void* gate_up, void* out, int rows, int inter, cudaStream_t stream) {
+// out = act(gate) * up of the two halves of gate_up's rows; kind 0 silu, 1 gelu in its tanh form
+TLIE_EXPORT int tlie_gate_mul(int dtype, const void* gate_up, void* out, int rows, int inter, int kind, cudaStream_t stream) {
+  if (kind < 0 || kind > 1) return (int)cudaErrorInvalidValue;
   const size_t total = (size_t)rows * inter;
   if (total == 0) return 0;
   if (inter % 4 == 0) {
@@ -354,17 +361,21 @@ TLIE_EXPORT int tlie_silu_mul(int dtype, const void* gate_up, void* out, int row
     const size_t most = (size_t)device_sm_count() * 32;
     const int blocks = (int)((total4 + 255) / 256 < most ? (total4 + 255) / 256 : most);
     if (dtype == TLIE_F32)
-      silu_mul_vec_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total4);
+      silu_mul_vec_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total4, kind);
     else
-      silu_mul_vec_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total4);
+      silu_mul_vec_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total4, kind);
     return (int)cudaGetLastError();
   }
   if (dtype == TLIE_F32)
-    silu_mul_kernel<float><<<grid_for(total, 256), 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+    silu_mul_kernel<float><<<grid_for(total, 256), 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total, kind);
   else
     silu_mul_kernel<__nv_bfloat16><<<grid_for(total, 256), 256, 0, stream>>>((const __nv_bfloat16*)gate_up,
-                                                                             (__nv_bfloat16*)out, inter, total);
+                                                                             (__nv_bfloat16*)out, inter, total, kind);
   return (int)cudaGetLastError();
+}
+
+TLIE_EXPORT int tlie_silu_mul(int dtype, const void* gate_up, void* out, int rows, int inter, cudaStream_t stream) {
+  return tlie_gate_mul(dtype, gate_up, out, rows, inter, 0, stream);
 }
 
 TLIE_EXPORT int tlie_embedding_positions(int dtype, const void* table, const void* place_table, const int* ids, const int* positions,

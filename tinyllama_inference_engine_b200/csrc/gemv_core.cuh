@@ -34,7 +34,7 @@ struct GemvArgs {
   // STORE_BF16 may apply an activation to the (rounded) product before it is stored: 0 none, 1 the square of relu, 2 gelu in its
   // tanh form, 3 silu.  The same roundings as a product stored and an elementwise kernel run over it.
   int activation;
-  // GATED: how the two halves meet.  gate_kind 0: silu(gate) * up.  1: with g = min(gate, gate_limit) and u = clamp(up, -gate_limit,
+  // GATED: how the two halves meet.  gate_kind 0: silu(gate) * up.  2: gelu (tanh form) of the gate times up.  1: with g = min(gate, gate_limit) and u = clamp(up, -gate_limit,
   // gate_limit): g * sigmoid(gate_alpha * g) * (u + gate_shift).
   int gate_kind;
   float gate_limit, gate_alpha, gate_shift;
@@ -186,6 +186,9 @@ __device__ __forceinline__ void gemv_reduce_store(const GemvArgs& a, const float
       if (a.gate_kind == 1) {
         const float g = fminf(gate, a.gate_limit), u = fminf(fmaxf(up, -a.gate_limit), a.gate_limit);
         reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(g * (1.0f / (1.0f + expf(-a.gate_alpha * g))) * (u + a.gate_shift));
+      } else if (a.gate_kind == 2) {
+        const float act = 0.5f * gate * (1.0f + tanhf(0.7978845608028654f * (gate + 0.044715f * gate * gate * gate)));
+        reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn(act * up);
       } else {
         reinterpret_cast<__nv_bfloat16*>(a.out)[o] = __float2bfloat16_rn((gate / (1.0f + expf(-gate))) * up);
       }

@@ -111,7 +111,7 @@ TLIE_EXPORT void tlie_gemv_set_wide_ctas(int on) { gemv_wide_ctas = on; }
 // [M, square_tiles] the rows' sums of squares, as an earlier call with epilogue 2 and prepare_* left them.
 // prepare_weight (epilogue 2 only, else null): also store bf16(out * prepare_weight) in prepare_x [M, N] and the rows' sums of
 // squares per 16 columns in prepare_squares [M, ceil(N / 16)].  epilogue 0: bf16 out [M, N]; 1: 32-bit out; 2: out (32-bit [M, N]) += result;
-// 3: w holds [gate rows | up rows] (N even), out = silu(gate) * up as bf16 [M, N / 2] (gate_kind 1: the halves clamped at gate_limit,
+// 3: w holds [gate rows | up rows] (N even), out = silu(gate) * up as bf16 [M, N / 2] (gate_kind 2: gelu in its tanh form in the place of silu; gate_kind 1: the halves clamped at gate_limit,
 // min(gate) * sigmoid(gate_alpha * min(gate)) * (clamp(up) + gate_shift)).  activation (epilogue 0 only): 1 the square of
 // relu, 2 gelu in its tanh form, 3 silu, applied to the rounded product before it is stored.
 // Needs K % 8 == 0 (K % 4 == 0 suffices for x_mode 1 is NOT enough: weights are read 8 at a time), M <= 16.
@@ -120,7 +120,7 @@ TLIE_EXPORT int tlie_gemv_fused(int x_mode, const void* x, int ldx, const int* r
                                 const float* prepare_weight, void* prepare_x, float* prepare_squares, int activation, int gate_kind, float gate_limit,
                                 float gate_alpha, float gate_shift, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (gate_kind < 0 || gate_kind > 1 || (gate_kind != 0 && epilogue != EPI_GATED)) return (int)cudaErrorInvalidValue;
+  if (gate_kind < 0 || gate_kind > 2 || (gate_kind != 0 && epilogue != EPI_GATED)) return (int)cudaErrorInvalidValue;
   if (activation < 0 || activation > 3 || (activation != 0 && epilogue != EPI_STORE_BF16)) return (int)cudaErrorInvalidValue;
   if (K <= 0 || K % 8 != 0 || M > 16 || ((x_mode == X_PLAIN || x_mode == X_PREPARED) && ldx % 8 != 0) || (epilogue == EPI_GATED && (N & 1)) ||
       (x_mode == X_PREPARED && (squares == nullptr || square_tiles <= 0)) ||

@@ -1,0 +1,268 @@
+// A feed-forward of routed experts: every token goes through ``top`` of ``experts`` small gated feed-forwards, chosen by a router.
+//
+//   moe_route     per token: z = W_router x (32-bit), s = sigmoid(z), choice = s + correction.  Experts form ``groups`` equal groups
+//                 of neighbours; a group's score is the sum of its two largest choice scores; only experts of the ``keep`` best
+//                 groups can be chosen.  The ``top`` largest choice scores among them are chosen (ties: the lower index); their
+//                 weights are s / (sum of the chosen s + 1e-20) * route_scale.
+//   moe_gate_up   per (token, chosen expert): act(W_gate x) * (W_up x), straight from the expert's rows (steps of few rows, and the
+//                 32-bit path): a warp per output, the sums in a fixed order.
+//   moe_down      per token: sum over its chosen experts of weight * W_down act, plus the shared branch if there is one.
+//
+// Expert weights are stacked: gate_up [experts][2 ff][width] (gate rows, then up rows), down [experts][width][ff].
+// Activation codes: 0 silu, 1 gelu in its tanh form.
+#include "common.cuh"
+
+namespace tlie {
+
+__device__ __forceinline__ float moe_act(float z, int kind) {
+  if (kind == 1) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return z / (1.0f + expf(-z));
+}
+
+// the lane's share of w . x: w a row of T in global memory, x 32-bit numbers in shared memory; 16 bytes at a time where rows allow it
+__device__ __forceinline__ float lane_dot(const float* w, const float* x, int width, int lane, bool vector) {
+  float sum = 0.0f;
+  if (vector) {
+    for (int d = lane * 4; d < width; d += 128) {
+      const float4 a = *reinterpret_cast<const float4*>(w + d);
+      sum = fmaf(a.x, x[d], sum);
+      sum = fmaf(a.y, x[d + 1], sum);
+      sum = fmaf(a.z, x[d + 2], sum);
+      sum = fmaf(a.w, x[d + 3], sum);
+    }
+  } else {
+    for (int d = lane; d < width; d += 32) sum = fmaf(w[d], x[d], sum);
+  }
+  return sum;
+}
+__device__ __forceinline__ float lane_dot(const __nv_bfloat16* w, const float* x, int width, int lane, bool vector) {
+  float sum = 0.0f;
+  if (vector) {
+    for (int d = lane * 8; d < width; d += 256) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(w + d);
+      const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 a = __bfloat1622float2(pairs[i]);
+        sum = fmaf(a.x, x[d + 2 * i], sum);
+        sum = fmaf(a.y, x[d + 2 * i + 1], sum);
+      }
+    }
+  } else {
+    for (int d = lane; d < width; d += 32) sum = fmaf(__bfloat162float(w[d]), x[d], sum);
+  }
+  return sum;
+}
+template <typename T>
+__device__ __forceinline__ bool rows_are_vectors(const T* base, int width) {
+  return width % (16 / (int)sizeof(T)) == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0;
+}
+
+// the largest of values[0 .. n) over the warp, the lower index on ties; every lane gets the answer
+__device__ __forceinline__ int warp_argmax(const float* values, int n, int lane, float& best_value) {
+  float best = -INFINITY;
+  int at = 0x7fffffff;
+  for (int i = lane; i < n; i += 32)
+    if (values[i] > best || at == 0x7fffffff) {
+      best = values[i];
+      at = i;
+    }
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+    const int other_at = __shfl_xor_sync(0xffffffffu, at, offset);
+    if (other_at != 0x7fffffff && (at == 0x7fffffff || other > best || (other == best && other_at < at))) {
+      best = other;
+      at = other_at;
+    }
+  }
+  best_value = best;
+  return at;
+}
+
+constexpr int kRouteWarps = 4;
+
+// a warp per token; shared memory per warp: s [experts], choice [experts], group scores [groups]
+template <typename T>
+__global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router, const float* __restrict__ correction,
+                                                                     int* __restrict__ ids, float* __restrict__ weights, int tokens, int width, int experts,
+                                                                     int groups, int keep, int top, float route_scale) {
+  extern __shared__ float route_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * kRouteWarps + warp;
+  if (t >= tokens) return;
+  float* s = route_smem + (size_t)warp * (2 * experts + groups);
+  float* choice = s + experts;
+  float* group_score = choice + experts;
+  const T* row = x + (size_t)t * width;
+  for (int e = 0; e < experts; ++e) {
+    const float* w = router + (size_t)e * width;
+    float sum = 0.0f;
+    for (int d = lane; d < width; d += 32) sum = fmaf(w[d], to_float(row[d]), sum);
+    sum = warp_sum(sum);
+    if (lane == 0) {
+      const float score = 1.0f / (1.0f + expf(-sum));
+      s[e] = score;
+      choice[e] = score + (correction != nullptr ? correction[e] : 0.0f);
+    }
+  }
+  __syncwarp();
+  const int per = experts / groups;
+  if (groups > 1 && keep < groups) {
+    for (int g = lane; g < groups; g += 32) {
+      float first = -INFINITY, second = -INFINITY;
+      for (int i = 0; i < per; ++i) {
+        const float c = choice[g * per + i];
+        if (c > first) {
+          second = first;
+          first = c;
+        } else if (c > second) {
+          second = c;
+        }
+      }
+      group_score[g] = per > 1 ? first + second : first;
+    }
+    __syncwarp();
+    // the ``keep`` best groups are marked by a score of +inf; the others' experts leave the choice
+    for (int round = 0; round < keep; ++round) {
+      float value;
+      // groups already taken hold +inf and would win again: pick among the rest
+      float best = -INFINITY;
+      int at = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32)
+        if (group_score[g] != INFINITY && (at == 0x7fffffff || group_score[g] > best)) {
+          best = group_score[g];
+          at = g;
+        }
+#pragma unroll
+      for (int offset = 16; offset > 0; offset >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+        const int other_at = __shfl_xor_sync(0xffffffffu, at, offset);
+        if (other_at != 0x7fffffff && (at == 0x7fffffff || other > best || (other == best && other_at < at))) {
+          best = other;
+          at = other_at;
+        }
+      }
+      (void)value;
+      if (lane == 0 && at != 0x7fffffff) group_score[at] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < experts; e += 32)
+      if (group_score[e / per] != INFINITY) choice[e] = -INFINITY;
+    __syncwarp();
+  }
+  float total = 0.0f;
+  for (int k = 0; k < top; ++k) {
+    float value;
+    const int e = warp_argmax(choice, experts, lane, value);
+    if (lane == 0) {
+      ids[(size_t)t * top + k] = e;
+      weights[(size_t)t * top + k] = s[e];
+      choice[e] = -INFINITY;
+    }
+    total += s[e];
+    __syncwarp();
+  }
+  const float factor = route_scale / (total + 1e-20f);
+  for (int k = lane; k < top; k += 32) weights[(size_t)t * top + k] *= factor;
+}
+
+constexpr int kMoeWarps = 8;
+constexpr int kGateUpOutputs = 32;   // outputs of one CTA of the direct first half
+constexpr int kDownOutputs = 32;
+
+// grid (tokens * top, ceil(ff / 32)); act [tokens * top][ff]
+template <typename T>
+__global__ void __launch_bounds__(kMoeWarps * 32) moe_gate_up_kernel(const T* __restrict__ x, const T* __restrict__ gate_up, const int* __restrict__ ids,
+                                                                     T* __restrict__ act, int width, int ff, int top, int kind) {
+  extern __shared__ float moe_x[];
+  const int slot = blockIdx.x, t = slot / top;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int d = threadIdx.x; d < width; d += blockDim.x) moe_x[d] = to_float(x[(size_t)t * width + d]);
+  __syncthreads();
+  const T* expert = gate_up + (size_t)ids[slot] * 2 * ff * width;
+  const bool vector = rows_are_vectors(expert, width);
+  for (int i = warp; i < kGateUpOutputs; i += kMoeWarps) {
+    const int f = blockIdx.y * kGateUpOutputs + i;
+    if (f >= ff) break;
+    const float g = warp_sum(lane_dot(expert + (size_t)f * width, moe_x, width, lane, vector));
+    const float u = warp_sum(lane_dot(expert + (size_t)(ff + f) * width, moe_x, width, lane, vector));
+    if (lane == 0) act[(size_t)slot * ff + f] = from_float<T>(moe_act(g, kind) * u);
+  }
+}
+
+// grid (tokens, ceil(width / 32)); out[t] = sum_k weight_k * W_down[e_k] act[t, k]  (+ shared[t])
+template <typename T>
+__global__ void __launch_bounds__(kMoeWarps * 32) moe_down_kernel(const T* __restrict__ act, const T* __restrict__ down, const int* __restrict__ ids,
+                                                                  const float* __restrict__ weights, const T* __restrict__ shared, T* __restrict__ out, int width,
+                                                                  int ff, int top) {
+  extern __shared__ float moe_act_rows[];   // [top][ff]
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < top * ff; i += blockDim.x) moe_act_rows[i] = to_float(act[(size_t)t * top * ff + i]);
+  __syncthreads();
+  const bool vector = rows_are_vectors(down, ff);
+  for (int i = warp; i < kDownOutputs; i += kMoeWarps) {
+    const int n = blockIdx.y * kDownOutputs + i;
+    if (n >= width) break;
+    float total = 0.0f;
+    for (int k = 0; k < top; ++k) {
+      const T* expert = down + ((size_t)ids[(size_t)t * top + k] * width + n) * ff;
+      total += weights[(size_t)t * top + k] * warp_sum(lane_dot(expert, moe_act_rows + (size_t)k * ff, ff, lane, vector));
+    }
+    if (shared != nullptr) total += to_float(shared[(size_t)t * width + n]);
+    if (lane == 0) out[(size_t)t * width + n] = from_float<T>(total);
+  }
+}
+
+}  // namespace tlie
+
+using namespace tlie;
+
+TLIE_EXPORT int tlie_moe_route(int dtype, const void* x, const float* router, const float* correction, int* ids, float* weights, int tokens, int width, int experts,
+                               int groups, int keep, int top, float route_scale, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (experts <= 0 || groups <= 0 || experts % groups != 0 || keep <= 0 || keep > groups || top <= 0 || top > keep * (experts / groups))
+    return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)kRouteWarps * (2 * experts + groups) * sizeof(float);
+  if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+  const int blocks = (tokens + kRouteWarps - 1) / kRouteWarps;
+  if (dtype == TLIE_F32)
+    moe_route_kernel<float><<<blocks, kRouteWarps * 32, smem, stream>>>((const float*)x, router, correction, ids, weights, tokens, width, experts, groups, keep, top, route_scale);
+  else
+    moe_route_kernel<__nv_bfloat16><<<blocks, kRouteWarps * 32, smem, stream>>>((const __nv_bfloat16*)x, router, correction, ids, weights, tokens, width, experts, groups,
+                                                                              keep, top, route_scale);
+  return (int)cudaGetLastError();
+}
+
+template <typename T>
+static int launch_moe_experts(const void* x, const void* gate_up, const void* down, const int* ids, const float* weights, const void* shared, void* act, void* out,
+                              int tokens, int width, int ff, int top, int kind, cudaStream_t stream) {
+  const size_t x_smem = (size_t)width * sizeof(float), act_smem = (size_t)top * ff * sizeof(float);
+  if (x_smem > 200 * 1024 || act_smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  cudaError_t e;
+  if (x_smem > 48 * 1024) {
+    e = cudaFuncSetAttribute(moe_gate_up_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)x_smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  if (act_smem > 48 * 1024) {
+    e = cudaFuncSetAttribute(moe_down_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)act_smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  moe_gate_up_kernel<T><<<dim3(tokens * top, (ff + kGateUpOutputs - 1) / kGateUpOutputs), kMoeWarps * 32, x_smem, stream>>>(
+      (const T*)x, (const T*)gate_up, ids, (T*)act, width, ff, top, kind);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return (int)e;
+  moe_down_kernel<T><<<dim3(tokens, (width + kDownOutputs - 1) / kDownOutputs), kMoeWarps * 32, act_smem, stream>>>(
+      (const T*)act, (const T*)down, ids, weights, (const T*)shared, (T*)out, width, ff, top);
+  return (int)cudaGetLastError();
+}
+
+// ``act``: scratch [tokens * top, ff] of ``dtype``; ``shared`` [tokens, width] or null; ``out`` [tokens, width].
+TLIE_EXPORT int tlie_moe_experts(int dtype, const void* x, const void* gate_up, const void* down, const int* ids, const float* weights, const void* shared, void* act,
+                                 void* out, int tokens, int width, int ff, int top, int kind, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if ((long long)tokens * top > 2147483647LL / 2 || kind < 0 || kind > 1) return (int)cudaErrorInvalidValue;
+  if (dtype == TLIE_F32) return launch_moe_experts<float>(x, gate_up, down, ids, weights, shared, act, out, tokens, width, ff, top, kind, stream);
+  return launch_moe_experts<__nv_bfloat16>(x, gate_up, down, ids, weights, shared, act, out, tokens, width, ff, top, kind, stream);
+}

@@ -1,0 +1,117 @@
+// Norms around a residual branch, for layers that normalise a sublayer's output before it joins the stream:
+//
+//   residual[t] += norm(y[t]) * post_weight          (if y is given)
+//   out[r]       = norm(residual[rows[r]]) * next_weight   (if out is given; rows null: every row in order)
+//
+// in one kernel, a CTA per row.  ``centred`` 1: (x - mean) / sqrt(mean((x - mean)^2) + eps), the layer norm without a bias;
+// 0: x / sqrt(mean(x^2) + eps).  The row waits in shared memory as 32-bit numbers between the passes; mean, variance (of
+// the deviations, after the mean is known), the sum into the stream and the second norm are 32-bit whatever y and out are
+// stored as.  The order of a row's sums depends on the block size alone.
+//
+// stream_with_embedding: out[t] = [residual[t] | table[ids[t]] * scale] rounded to out's type: the operand of a product that
+// mixes the stream with the embedding's output.
+#include "common.cuh"
+
+namespace tlie {
+
+constexpr int kNormThreads = 256;
+
+__device__ __forceinline__ void row_statistics(const float* row, int width, int centred, float eps, float* scratch, float& mean, float& inv) {
+  mean = 0.0f;
+  if (centred) {
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) sum += row[i];
+    mean = block_sum(sum, scratch) / (float)width;
+  }
+  float squares = 0.0f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float d = row[i] - mean;
+    squares += d * d;
+  }
+  inv = 1.0f / sqrtf(block_sum(squares, scratch) / (float)width + eps);
+}
+
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(kNormThreads) branch_norm_kernel(float* __restrict__ residual, const TY* __restrict__ y, const float* __restrict__ post_weight,
+                                                                   const float* __restrict__ next_weight, TO* __restrict__ out, const int* __restrict__ rows,
+                                                                   float eps, int centred, int width) {
+  extern __shared__ float norm_row[];
+  __shared__ float scratch[32];
+  const int source = rows != nullptr ? rows[blockIdx.x] : blockIdx.x;
+  float* stream = residual + (size_t)source * width;
+  float mean, inv;
+  if (y != nullptr) {
+    const TY* branch = y + (size_t)source * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) norm_row[i] = to_float(branch[i]);
+    __syncthreads();
+    row_statistics(norm_row, width, centred, eps, scratch, mean, inv);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {   // every thread rereads what it wrote itself
+      const float v = stream[i] + ((norm_row[i] - mean) * inv) * post_weight[i];
+      stream[i] = v;
+      norm_row[i] = v;
+    }
+  } else {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) norm_row[i] = stream[i];
+  }
+  if (out == nullptr) return;
+  __syncthreads();
+  row_statistics(norm_row, width, centred, eps, scratch, mean, inv);
+  TO* dst = out + (size_t)blockIdx.x * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_float<TO>(((norm_row[i] - mean) * inv) * next_weight[i]);
+}
+
+template <typename T>
+__global__ void stream_with_embedding_kernel(const float* __restrict__ residual, const T* __restrict__ table, const int* __restrict__ ids, float scale,
+                                             T* __restrict__ out, int width, int vocab, int* __restrict__ error_flag) {
+  const int row = blockIdx.x;
+  int id = ids[row];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0 && error_flag != nullptr) atomicOr(error_flag, 2);
+    id = 0;
+  }
+  const float* stream = residual + (size_t)row * width;
+  const T* token = table + (size_t)id * width;
+  T* dst = out + (size_t)row * 2 * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    dst[i] = from_float<T>(stream[i]);
+    dst[width + i] = from_float<T>(to_float(token[i]) * scale);
+  }
+}
+
+template <typename TY, typename TO>
+static int launch_branch_norm(float* residual, const void* y, const float* post_weight, const float* next_weight, void* out, const int* rows, float eps,
+                              int centred, int count, int width, cudaStream_t stream) {
+  const size_t smem = (size_t)width * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(branch_norm_kernel<TY, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  branch_norm_kernel<TY, TO><<<count, kNormThreads, smem, stream>>>(residual, (const TY*)y, post_weight, next_weight, (TO*)out, rows, eps, centred, width);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace tlie
+
+using namespace tlie;
+
+// ``count`` rows are worked on: all of the stream's, or with ``rows`` the listed ones (then y must be null: a gathered norm adds nothing).
+// ``y`` and ``out`` are of ``dtype``; either may be null.
+TLIE_EXPORT int tlie_branch_norm(int dtype, float* residual, const void* y, const float* post_weight, const float* next_weight, void* out, const int* rows,
+                                 float eps, int centred, int count, int width, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  if (width <= 0 || (rows != nullptr && y != nullptr) || (y != nullptr && post_weight == nullptr) || (out != nullptr && next_weight == nullptr))
+    return (int)cudaErrorInvalidValue;
+  if (dtype == TLIE_F32) return launch_branch_norm<float, float>(residual, y, post_weight, next_weight, out, rows, eps, centred, count, width, stream);
+  return launch_branch_norm<__nv_bfloat16, __nv_bfloat16>(residual, y, post_weight, next_weight, out, rows, eps, centred, count, width, stream);
+}
+
+TLIE_EXPORT int tlie_stream_with_embedding(int dtype, const float* residual, const void* table, const int* ids, float scale, void* out, int rows, int width,
+                                           int vocab, int* error_flag, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (dtype == TLIE_F32)
+    stream_with_embedding_kernel<float><<<rows, 256, 0, stream>>>(residual, (const float*)table, ids, scale, (float*)out, width, vocab, error_flag);
+  else
+    stream_with_embedding_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>(residual, (const __nv_bfloat16*)table, ids, scale, (__nv_bfloat16*)out, width, vocab, error_flag);
+  return (int)cudaGetLastError();
+}

@@ -18,10 +18,12 @@ import torch
 from ..errors import KernelError
 from .build import build_library, load_library
 
-CORE_SOURCES = ["elementwise.cu", "rowwise.cu", "rope_cache.cu", "attention_generic.cu", "gemm_fp32.cu", "sampling.cu"]
+CORE_SOURCES = ["elementwise.cu", "rowwise.cu", "norm_branch.cu", "rope_cache.cu", "attention_generic.cu", "gemm_fp32.cu", "sampling.cu"]
 RECURRENT_SOURCES = ["recurrent.cu"]              # compiled when a model with a recurrent mixer is first stepped
 MIXED_ATTENTION_SOURCES = ["attention_mixed.cu"]   # likewise for attention with a distance bias, mixed heads or an output gate
 DELTA_RULE_SOURCES = ["delta_rule.cu"]             # likewise for the gated delta rule
+DIFF_ATTENTION_SOURCES = ["attention_diff.cu"]     # likewise for differential attention
+MOE_SOURCES = ["moe.cu"]                           # likewise for a feed-forward of routed experts
 _F32, _BF16 = 0, 1
 launch_count = 0  # kernels of this engine launched by this process (a claim the bench reports)
 
@@ -38,7 +40,8 @@ def core():
 def build_all() -> list:
     """Compile every kernel set (used by the build check); returns the library paths."""
     return [build_library("tlie_core", CORE_SOURCES), build_library("tlie_recurrent", RECURRENT_SOURCES),
-            build_library("tlie_attention_mixed", MIXED_ATTENTION_SOURCES), build_library(f"tlie_delta_rule_l{DELTA_LANES}", DELTA_RULE_SOURCES, {"TLIE_DELTA_LANES": DELTA_LANES})] + fast.build_all()
+            build_library("tlie_attention_mixed", MIXED_ATTENTION_SOURCES), build_library(f"tlie_delta_rule_l{DELTA_LANES}", DELTA_RULE_SOURCES, {"TLIE_DELTA_LANES": DELTA_LANES}),
+            build_library("tlie_attention_diff", DIFF_ATTENTION_SOURCES), build_library("tlie_moe", MOE_SOURCES)] + fast.build_all()
 
 
 def _code(tensor: torch.Tensor) -> int:
@@ -187,6 +190,47 @@ def silu_mul(gate_up, out) -> None:
     if gate_up.shape != (rows, 2 * inter) or gate_up.dtype != out.dtype:
         raise KernelError("silu_mul: gate_up must be [rows, 2 * inter] of the output's dtype", code="invalid_shape")
     _check(core().tlie_silu_mul(_code(out), _ptr(gate_up), _ptr(out), c_int(rows), c_int(inter), _stream()), "silu_mul")
+
+
+GATE_KINDS = {"silu": 0, "gelu_tanh": 1}
+
+
+def gate_mul(gate_up, out, kind: str = "silu") -> None:
+    """out = act(gate) * up for the two halves of ``gate_up``'s rows, 32-bit inside; ``kind``: "silu" or "gelu_tanh"."""
+    rows, inter = out.shape
+    if gate_up.shape != (rows, 2 * inter) or gate_up.dtype != out.dtype or kind not in GATE_KINDS:
+        raise KernelError("gate_mul: gate_up must be [rows, 2 * inter] of the output's dtype, kind one of " + ", ".join(GATE_KINDS), code="invalid_shape")
+    _check(core().tlie_gate_mul(_code(out), _ptr(gate_up), _ptr(out), c_int(rows), c_int(inter), c_int(GATE_KINDS[kind]), _stream()), "gate_mul")
+
+
+def branch_norm(residual, y, post_weight, next_weight, out, eps: float, centred: bool = True, rows=None) -> None:
+    """One kernel around a residual branch: ``residual += norm(y) * post_weight`` (if ``y`` is given), then
+    ``out = norm(residual[rows]) * next_weight`` (if ``out`` is given; ``rows`` None: every row in order, and only then may ``y`` be given).
+    ``centred``: the layer norm without a bias, (x - mean) / sqrt(mean((x - mean)^2) + eps); else x / sqrt(mean(x^2) + eps).
+    The stream, the statistics and the weights are 32-bit; ``y`` and ``out`` share a dtype."""
+    width = residual.shape[1]
+    count = residual.shape[0] if rows is None else rows.shape[0]
+    if residual.dtype != torch.float32 or (y is not None and (y.shape != residual.shape or rows is not None)) or (out is not None and out.shape != (count, width)):
+        raise KernelError("branch_norm: a 32-bit stream [T, width], y of its shape, out [rows, width]", code="invalid_shape")
+    for weight in (post_weight, next_weight):
+        if weight is not None and (weight.dtype != torch.float32 or weight.numel() != width):
+            raise KernelError("branch_norm: norm weights are 32-bit [width]", code="invalid_shape")
+    if y is not None and out is not None and y.dtype != out.dtype:
+        raise KernelError("branch_norm: y and out share a dtype", code="invalid_dtype")
+    if y is None and out is None:
+        return
+    _check(core().tlie_branch_norm(_code(y if y is not None else out), _ptr(residual), _ptr(y), _ptr(post_weight if y is not None else None),
+                                   _ptr(next_weight if out is not None else None), _ptr(out), _i32(rows, "rows"), c_float(eps), c_int(1 if centred else 0),
+                                   c_int(count), c_int(width), _stream()), "branch_norm")
+
+
+def stream_with_embedding(residual, table, ids, scale: float, out) -> None:
+    """out[t] = [residual[t] | table[ids[t]] * scale], rounded to ``out``'s dtype (the table's): the stream beside the embedding's output."""
+    rows, width = residual.shape
+    if residual.dtype != torch.float32 or table.shape[1] != width or out.shape != (rows, 2 * width) or out.dtype != table.dtype:
+        raise KernelError("stream_with_embedding: a 32-bit stream [T, width], a table [vocab, width], out [T, 2 width] of the table's dtype", code="invalid_shape")
+    _check(core().tlie_stream_with_embedding(_code(out), _ptr(residual), _ptr(table), _i32(ids, "ids"), c_float(scale), _ptr(out), c_int(rows), c_int(width),
+                                             c_int(table.shape[0]), _ptr(error_flag(residual.device)), _stream()), "stream_with_embedding")
 
 
 def add_row_vector(residual, delta, vector) -> None:
@@ -396,8 +440,20 @@ def linear_accumulate(x, weight, residual, prepare: "LazyNorm | None" = None) ->
         add_(residual, delta)
 
 
-def linear_gated(x, weight, out, clamp=None) -> None:
-    """out = silu(x . gate^T) * (x . up^T) for weight = [gate rows | up rows], in one kernel (``clamp``: see ``norm_linear``)."""
+def linear_gated(x, weight, out, clamp=None, activation: str = "silu") -> None:
+    """out = act(x . gate^T) * (x . up^T) for weight = [gate rows | up rows], in one kernel where one takes the shape (``clamp``: see
+    ``norm_linear``; ``activation``: "silu", or "gelu_tanh", which the small-step kernel has in its epilogue and larger steps run
+    as a kernel behind the product)."""
+    if activation != "silu":
+        if activation not in GATE_KINDS or clamp is not None:
+            raise KernelError(f"linear_gated: no gate {activation!r} (with a clamp: silu only)", code="invalid_argument")
+        if x.dtype == torch.bfloat16 and fast.gemv_fits(x.shape[0], weight.shape[1], norm=False, gated=True) and x.stride(1) == 1 and x.stride(0) % 8 == 0:
+            fast.gemv_fused(x, weight, out, epilogue="gated", gate=activation)
+            return
+        gate_up = torch.empty((x.shape[0], weight.shape[0]), dtype=x.dtype, device=x.device)
+        linear(x, weight, gate_up)
+        gate_mul(gate_up, out, activation)
+        return
     if x.dtype == torch.bfloat16 and fast.gemv_fits(x.shape[0], weight.shape[1], norm=False, gated=True):
         fast.gemv_fused(x, weight, out, epilogue="gated", clamp=clamp)
     elif clamp is not None:
@@ -695,6 +751,110 @@ def mixed_heads_attention(rows, gate_offset: int, positions, token_seq, cache, s
                                                         c_int(key_dim), c_int(value_dim), c_int(cache.page_size), c_int(window), c_float(scale), c_int(splits), _ptr(partial),
                                                         c_int(keep_first if window > 0 else 0), c_int(1 if gate_per_head else 0), _ptr(sinks), c_int(v_row_stride), _stream()),
            "mixed_heads_attention")
+
+
+# --- differential attention --------------------------------------------------------------------
+def diff_attention_library():
+    return load_library("tlie_attention_diff", DIFF_ATTENTION_SOURCES)
+
+
+def _diff_planes(cache, kv_heads: int, dim: int, vdim: int):
+    """The key plane (two vectors per key/value head: one per map) and the value plane of a layer's pages."""
+    if len(cache.plane_pages) != 2:
+        raise KernelError("differential attention keeps a key plane [pages, 2 kv heads, page size, dim] and a value plane [pages, kv heads, page size, vdim]", code="invalid_shape")
+    k_pages, v_pages = cache.plane_pages
+    if tuple(k_pages.shape[1:]) != (2 * kv_heads, cache.page_size, dim) or tuple(v_pages.shape[1:]) != (kv_heads, cache.page_size, vdim) or k_pages.dtype != v_pages.dtype:
+        raise KernelError("differential attention keeps a key plane [pages, 2 kv heads, page size, dim] and a value plane [pages, kv heads, page size, vdim]", code="invalid_shape")
+    return k_pages, v_pages, 2 * kv_heads * cache.page_size * dim, kv_heads * cache.page_size * vdim
+
+
+def diff_store(rows, k_offset: int, v_offset: int, q_weight, k_weight, eps: float, inv_freq, rot_dims: int, positions, token_seq, cache, heads: int, kv_heads: int,
+               dim: int, vdim: int) -> None:
+    """Differential attention's norm, rotation and cache write.  ``rows`` [T, >= 2 heads dim + 2 kv dim + kv vdim]: queries head by head as
+    [map 1 | map 2], keys from ``k_offset`` laid out the same way, values from ``v_offset``.  Every query and key vector is divided by its root
+    mean square (``eps`` inside the root) and multiplied by a 32-bit weight [dim]; then its first ``rot_dims`` columns turn, column i with
+    column i + rot_dims / 2, by position * inv_freq[i].  Queries are left in place; keys and values go into the token's pages."""
+    k_pages, v_pages, k_stride, v_stride = _diff_planes(cache, kv_heads, dim, vdim)
+    if k_pages.dtype != rows.dtype or inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dims // 2 or rot_dims % 2 or rot_dims > dim:
+        raise KernelError("diff_store: pages of the rows' dtype; inv_freq 32-bit [rot_dims / 2], rot_dims even and at most dim", code="invalid_shape")
+    for weight in (q_weight, k_weight):
+        if weight.dtype != torch.float32 or weight.numel() != dim:
+            raise KernelError("diff_store: the query and key norms' weights are 32-bit [dim]", code="invalid_shape")
+    table = cache.block_table
+    _check(diff_attention_library().tlie_diff_store(_code(rows), _ptr(rows), c_int(rows.shape[1]), c_int(k_offset), c_int(v_offset), _ptr(q_weight), _ptr(k_weight),
+                                                    c_float(eps), _ptr(inv_freq), c_int(rot_dims), _i32(positions, "positions"), _i32(token_seq, "token_seq"),
+                                                    _i32(table, "block_table"), c_int(table.shape[1]), _ptr(k_pages), c_longlong(k_stride), _ptr(v_pages),
+                                                    c_longlong(v_stride), c_int(rows.shape[0]), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim),
+                                                    c_int(cache.page_size), c_int(1 if cache.writes else 0), _stream()), "diff_store")
+
+
+def diff_attention(rows, positions, token_seq, cache, out, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, lam: float, eps: float, out_scale: float,
+                   batch=None) -> None:
+    """Causal differential attention over the paged keys.  Head h has two maps, softmax(scale q_m . k_m) v for m = 1, 2 over the same
+    values (query vectors 2 h and 2 h + 1 of ``rows``, key vectors 2 g and 2 g + 1 of key/value head g = h // (heads / kv_heads));
+    out_h = o / sqrt(mean(o^2) + eps) * out_scale with o = map 1 - lam * map 2.  ``batch``: the step's context, from which the kernel and
+    the number of runs a row's keys are cut into are chosen."""
+    tokens = rows.shape[0]
+    if heads % kv_heads != 0 or out.shape != (tokens, heads * vdim) or out.dtype != rows.dtype:
+        raise KernelError("diff_attention: out must be [rows, heads * vdim] of the rows' dtype, heads a multiple of kv heads", code="invalid_shape")
+    k_pages, v_pages, k_stride, v_stride = _diff_planes(cache, kv_heads, dim, vdim)
+    if k_pages.dtype != rows.dtype:
+        raise KernelError("diff_attention: pages and rows differ in dtype", code="invalid_dtype")
+    table = cache.block_table
+    if rows.dtype == torch.bfloat16 and fast.diff_prefill_takes(batch, rows, cache.page_size, dim, vdim):
+        fast.diff_prefill(rows, batch, table, (k_pages, k_stride, v_pages, v_stride), out, heads, kv_heads, dim, vdim, cache.page_size, scale, lam, eps, out_scale)
+        return
+    runs = 1
+    if batch is not None and tokens * kv_heads * 2 <= fast.sm_count():
+        runs = max(1, min(2 * fast.sm_count() // (tokens * kv_heads), -(-batch.max_seq_len // 32), 64))   # down to one tile of 32 keys per CTA
+    parts = fast.mixed_scratch(rows.device, tokens * runs * 2 * heads * (vdim + 2), torch.float32)
+    _check(diff_attention_library().tlie_diff_attention(_code(rows), _ptr(rows), c_int(rows.shape[1]), _ptr(k_pages), c_longlong(k_stride), _ptr(v_pages),
+                                                        c_longlong(v_stride), _i32(positions, "positions"), _i32(token_seq, "token_seq"), _i32(table, "block_table"),
+                                                        c_int(table.shape[1]), _ptr(parts), _ptr(out), c_int(tokens), c_int(heads), c_int(kv_heads), c_int(dim),
+                                                        c_int(vdim), c_int(cache.page_size), c_float(scale), c_float(lam), c_float(eps), c_float(out_scale),
+                                                        c_int(runs), _stream()), "diff_attention")
+
+
+# --- routed experts ------------------------------------------------------------------------------
+def moe_library():
+    return load_library("tlie_moe", MOE_SOURCES)
+
+
+def moe_route(x, router, correction, ids, weights, groups: int, keep: int, route_scale: float) -> None:
+    """Per token of ``x`` [T, width]: s = sigmoid(router x) (``router`` 32-bit [experts, width], sums in 32-bit), choice = s + ``correction``
+    (32-bit [experts] or None).  Experts form ``groups`` equal groups of neighbours; a group's score is the sum of its two largest choice
+    scores and only experts of the ``keep`` best groups can be chosen.  ``ids`` int32 [T, top] receives the experts of the ``top`` largest
+    choice scores (the lower index on ties), ``weights`` 32-bit [T, top] their s / (sum of the chosen s + 1e-20) * ``route_scale``."""
+    tokens, width = x.shape
+    experts, top = router.shape[0], ids.shape[1]
+    if router.dtype != torch.float32 or router.shape[1] != width or ids.dtype != torch.int32 or ids.shape != (tokens, top) or weights.dtype != torch.float32 or weights.shape != (tokens, top):
+        raise KernelError("moe_route: a 32-bit router [experts, width], int32 ids and 32-bit weights [T, top]", code="invalid_shape")
+    if correction is not None and (correction.dtype != torch.float32 or correction.numel() != experts):
+        raise KernelError("moe_route: the correction is 32-bit [experts]", code="invalid_shape")
+    _check(moe_library().tlie_moe_route(_code(x), _ptr(x), _ptr(router), _ptr(correction), _ptr(ids), _ptr(weights), c_int(tokens), c_int(width), c_int(experts),
+                                        c_int(groups), c_int(keep), c_int(top), c_float(route_scale), _stream()), "moe_route")
+
+
+def moe_experts(x, gate_up, down, ids, weights, shared, out, activation: str = "silu", batch=None) -> None:
+    """out[t] = sum_k weights[t, k] * W_down[e] (act(W_gate[e] x[t]) * (W_up[e] x[t])) for e = ids[t, k], plus ``shared[t]`` if given.
+    ``gate_up`` [experts, 2 ff, width] (an expert's gate rows, then its up rows), ``down`` [experts, width, ff].  Steps of few rows and the
+    32-bit path read each chosen expert's rows directly; bfloat16 prompt portions sort the (token, expert) pairs by expert and run
+    the experts' products on the tensor cores."""
+    tokens, width = x.shape
+    experts, two_ff, _ = gate_up.shape
+    ff, top = two_ff // 2, ids.shape[1]
+    if gate_up.shape != (experts, 2 * ff, width) or down.shape != (experts, width, ff) or out.shape != (tokens, width) or gate_up.dtype != x.dtype or down.dtype != x.dtype or out.dtype != x.dtype:
+        raise KernelError("moe_experts: gate_up [experts, 2 ff, width], down [experts, width, ff], out [T, width], one dtype", code="invalid_shape")
+    if shared is not None and (shared.shape != out.shape or shared.dtype != out.dtype):
+        raise KernelError("moe_experts: the shared branch has the output's shape and dtype", code="invalid_shape")
+    if activation not in GATE_KINDS:
+        raise KernelError(f"moe_experts: no activation {activation!r}", code="invalid_argument")
+    if x.dtype == torch.bfloat16 and fast.moe_grouped_takes(tokens, top, width, ff):
+        fast.moe_grouped(x, gate_up, down, ids, weights, shared, out, GATE_KINDS[activation])
+        return
+    act = fast.mixed_scratch(x.device, tokens * top * ff, x.dtype)
+    _check(moe_library().tlie_moe_experts(_code(x), _ptr(x), _ptr(gate_up), _ptr(down), _ptr(ids), _ptr(weights), _ptr(shared), _ptr(act), _ptr(out), c_int(tokens),
+                                          c_int(width), c_int(ff), c_int(top), c_int(GATE_KINDS[activation]), _stream()), "moe_experts")
 
 
 # --- sampling ------------------------------------------------------------------------------

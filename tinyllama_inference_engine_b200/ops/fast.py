@@ -98,7 +98,10 @@ def prepared_norm_buffers(rows: int, width: int, device) -> tuple:
 GEMV_ACTIVATIONS = {None: 0, "relu_squared": 1, "gelu_tanh": 2, "silu": 3}
 
 
-def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store", prepared=None, prepare=None, activation: str | None = None, clamp=None) -> None:
+GEMV_GATES = {"silu": 0, "gelu_tanh": 2}   # the gated epilogue's activation (1 is the clamped gate, chosen by ``clamp``)
+
+
+def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store", prepared=None, prepare=None, activation: str | None = None, clamp=None, gate: str = "silu") -> None:
     """out (+)= f(x) . weight^T for up to 16 rows, one kernel.
 
     norm      None: ``x`` is bfloat16 [M, K].  (norm_weight, eps, rows): ``x`` is the 32-bit residual stream and
@@ -107,7 +110,8 @@ def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store", prepared=N
               squares, as an earlier "accumulate" with ``prepare`` left them; the operand is the same rmsnorm.
     epilogue  "store": out [M, N] bfloat16 or 32-bit;  "accumulate": out is the 32-bit residual, out += result;
               "gated": weight is [gate rows | up rows], out [M, N / 2] = silu(gate) * up; with ``clamp`` = (limit, alpha, shift) instead
-              g * sigmoid(alpha * g) * (u + shift) for g = min(gate, limit), u = clamp(up, -limit, limit).
+              g * sigmoid(alpha * g) * (u + shift) for g = min(gate, limit), u = clamp(up, -limit, limit); with ``gate`` = "gelu_tanh" the gate's
+              activation is gelu in its tanh form.
     activation ("store" into bfloat16 only) "relu_squared", "gelu_tanh" or "silu": applied to the rounded product before it is stored.
     prepare   ("accumulate" only) (norm_weight [N], x_out bfloat16 [M, N], squares_out [M, ceil(N / 16)]): also store
               bfloat16(out * norm_weight) and the rows' sums of squares per 16 columns, for a later call with ``prepared``.
@@ -152,7 +156,7 @@ def gemv_fused(x, weight, out, *, norm=None, epilogue: str = "store", prepared=N
             raise KernelError("gemv_fused: prepare takes a 32-bit norm weight [N], bfloat16 [M, N] and 32-bit [M, ceil(N / 16)], with accumulate", code="invalid_shape")
         emit = (ops._ptr(norm_weight), ops._ptr(x_out), ops._ptr(squares_out))
     ops._check(gemv_library().tlie_gemv_fused(*args, ops._ptr(weight), ops._ptr(out), c_int(M), c_int(N), c_int(K), c_int(code), *consume, *emit, c_int(GEMV_ACTIVATIONS[activation]),
-                                             c_int(0 if clamp is None else 1), *(c_float(float(v)) for v in (clamp or (0.0, 0.0, 0.0))), ops._stream()),
+                                             c_int(GEMV_GATES[gate] if clamp is None else 1), *(c_float(float(v)) for v in (clamp or (0.0, 0.0, 0.0))), ops._stream()),
                "gemv_fused")
 
 
@@ -839,3 +843,26 @@ def mixed_decode(rows, gate_offset: int, positions, token_seq, block_table, plan
 
 if os.environ.get("TLIE_SKINNY", "0") == "1":
     enable_skinny(True)
+
+
+# --- scratch by name ---------------------------------------------------------------------------
+_named_scratch: dict = {}
+
+
+def named_scratch(device: torch.device, name: str, elements: int, dtype: torch.dtype) -> torch.Tensor:
+    """Scratch that several kernels of one step hold at the same time, one buffer per name: of stable address, grown by adding a larger
+    one and never freed, since a captured graph may still point at an earlier one."""
+    held = _named_scratch.setdefault((device, name, dtype), [])
+    if not held or held[-1].numel() < elements:
+        held.append(torch.empty(max(elements, 1 << 16), dtype=dtype, device=device))
+    return held[-1][:elements]
+
+
+# --- differential attention on the tensor cores ---------------------------------------------------
+def diff_prefill_takes(batch, rows, page_size: int, dim: int, vdim: int) -> bool:
+    return False
+
+
+# --- routed experts on the tensor cores -------------------------------------------------------------
+def moe_grouped_takes(tokens: int, top: int, width: int, ff: int) -> bool:
+    return False

@@ -354,7 +354,83 @@ class LatentAttention(Mixer):
         return out
 
 
+class DifferentialAttention(Mixer):
+    """Attention whose every head takes the difference of two softmax maps over the same values.
+
+    q has ``num_heads`` x 2 vectors of ``key_dim`` and k has ``num_kv_heads`` x 2, head by head as [map 1 | map 2]; v has ``num_kv_heads``
+    vectors of ``value_dim``.  Every q and k vector passes an RMS norm with a weight ([key_dim], one for q and one for k, shared by all
+    heads and maps) and then a rotation of its first ``rot_dims`` columns (column i with column i + rot_dims / 2, by position *
+    rot_base^(-2 i / rot_dims)).  Per head: a_m = softmax(scale q_m . k_m) v (causal) for m = 1, 2, o = a_1 - lambda a_2 with
+    lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + ``diff`` (one number for the layer, from four stored vectors), then
+    o / sqrt(mean(o^2) + eps) * (1 - ``diff``); W_o on the concatenated heads.
+
+    params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``key_dim``, ``value_dim``, ``scale``, ``eps``, ``diff``, ``rot_dims``, ``rot_base``.
+    tensors: ``<prefix>.q`` [2 heads key_dim, hidden], ``<prefix>.k`` [2 kv key_dim, hidden], ``<prefix>.v`` [kv value_dim, hidden], ``<prefix>.q.norm``,
+    ``<prefix>.k.norm`` [key_dim], ``<prefix>.{lq1,lk1,lq2,lk2}`` [key_dim], ``<prefix>.o`` [hidden, heads value_dim].  q, k and v are one stacked
+    product.  The cache holds a key plane of 2 kv vectors per token (normalised and rotated) and a value plane of kv vectors.
+    Norms, angles, scores, softmax, the difference and its norm are 32-bit.
+    """
+
+    capturable = True
+
+    @classmethod
+    def _sizes(cls, spec: PartSpec) -> tuple[int, int, int, int, int]:
+        return int(spec["hidden_size"]), int(spec["num_heads"]), int(spec["num_kv_heads"]), int(spec["key_dim"]), int(spec["value_dim"])
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
+        hidden, heads, kv, dim, vdim = cls._sizes(spec)
+        std = hidden ** -0.5
+        specs = [TensorSpec(f"{prefix}.q", (2 * heads * dim, hidden), std=std), TensorSpec(f"{prefix}.k", (2 * kv * dim, hidden), std=std),
+                 TensorSpec(f"{prefix}.v", (kv * vdim, hidden), std=std), TensorSpec(f"{prefix}.q.norm", (dim,), init="norm", std=0.1),
+                 TensorSpec(f"{prefix}.k.norm", (dim,), init="norm", std=0.1)]
+        specs += [TensorSpec(f"{prefix}.{name}", (dim,), std=0.1) for name in ("lq1", "lk1", "lq2", "lk2")]
+        return specs + [TensorSpec(f"{prefix}.o", (hidden, heads * vdim), std=(heads * vdim) ** -0.5)]
+
+    @classmethod
+    def cache_need(cls, spec: PartSpec) -> CacheNeed:
+        _, _, kv, dim, vdim = cls._sizes(spec)
+        return CacheNeed("pages", planes=((2 * kv, dim), (kv, vdim)))
+
+    def __init__(self, spec, prefix, weights, runtime):
+        super().__init__(spec, prefix, weights, runtime)
+        self.hidden, self.heads, self.kv_heads, self.dim, self.vdim = self._sizes(spec)
+        self.scale, self.eps, self.diff = float(spec["scale"]), float(spec["eps"]), float(spec["diff"])
+        self.rot_dims = int(spec.get("rot_dims", 0) or 0)
+        dtype = runtime.dtype
+        stacked = [weights.get(f"{prefix}.{n}", dtype) for n in ("q", "k", "v")]
+        self.k_offset = 2 * self.heads * self.dim
+        self.v_offset = self.k_offset + 2 * self.kv_heads * self.dim
+        width = self.v_offset + self.kv_heads * self.vdim
+        if width % 8:   # rows of the stacked product start on 16-byte boundaries
+            stacked.append(torch.zeros((8 - width % 8, self.hidden), dtype=dtype, device=stacked[0].device))
+        self.w_in = torch.cat(stacked, dim=0).contiguous()
+        self.w_o = weights.get(f"{prefix}.o", dtype).contiguous()
+        self.q_weight = weights.get(f"{prefix}.q.norm", torch.float32).contiguous()
+        self.k_weight = weights.get(f"{prefix}.k.norm", torch.float32).contiguous()
+        # lambda: one number for the layer, worked out once in 32-bit
+        l = {name: weights.get(f"{prefix}.{name}", torch.float32) for name in ("lq1", "lk1", "lq2", "lk2")}
+        self.lam = float(torch.exp((l["lq1"] * l["lk1"]).sum()) - torch.exp((l["lq2"] * l["lk2"]).sum())) + self.diff
+        # frequencies in 64-bit, rounded once: the angle is float(position) * frequency in 32-bit inside the kernel
+        exponent = -2.0 * np.arange(self.rot_dims // 2, dtype=np.float64) / float(max(self.rot_dims, 1))
+        self.inv_freq = torch.from_numpy(np.power(float(spec.get("rot_base", 10000.0)), exponent).astype(np.float32)).to(runtime.device)
+
+    def forward(self, x, ctx, cache: LayerCache):
+        ws, dtype, tokens = self.runtime.workspace, self.runtime.dtype, x.shape[0]
+        rows = ws.get("diff_qkv", tokens, self.w_in.shape[0], dtype)
+        ops.linear(x, self.w_in, rows)
+        ops.diff_store(rows, self.k_offset, self.v_offset, self.q_weight, self.k_weight, self.eps, self.inv_freq, self.rot_dims, ctx.positions, ctx.token_seq, cache,
+                       self.heads, self.kv_heads, self.dim, self.vdim)
+        mixed = ws.get("attention", tokens, self.heads * self.vdim, dtype)
+        ops.diff_attention(rows, ctx.positions, ctx.token_seq, cache, mixed, self.heads, self.kv_heads, self.dim, self.vdim, self.scale, self.lam, self.eps,
+                           1.0 - self.diff, batch=ctx)
+        out = ws.get("mixer_out", tokens, self.hidden, dtype)
+        ops.linear(mixed, self.w_o, out)
+        return out
+
+
 register_part("mixer", "attention", Attention)
+register_part("mixer", "differential_attention", DifferentialAttention)
 register_part("mixer", "mixed_heads_attention", MixedHeadsAttention)
 register_part("mixer", "normed_key_attention", NormedKeyAttention)
 register_part("mixer", "latent_attention", LatentAttention)

@@ -95,5 +95,112 @@ class StreamVectorBlock(Block):
         return residual, None
 
 
+class SandwichNormBlock(Block):
+    """x -> x + post(mixer(pre(x))) -> x + post'(feed_forward(pre'(x))): a norm before every sublayer and another on its output,
+    before that joins the stream.
+
+    params: ``mixer``, ``feed_forward`` (or None), and the four norms ``mixer_norm``, ``mixer_post_norm``, ``feed_forward_norm``,
+    ``feed_forward_post_norm`` (PartSpecs of a norm kind that offers ``join``), each with its tensor-name suffix (``*_name``).
+    A branch's norm, its sum into the 32-bit stream and the norm that reads the stream next are one kernel (``Norm.join``); the norm
+    that follows the block's last sublayer is the next block's first one, which the block is told (``next_norm``) and hands over
+    finished, as a prepared norm, if it is of the same kind.
+    """
+
+    _SLOTS = (("mixer_norm", "norm"), ("mixer", "mixer"), ("mixer_post_norm", "norm"), ("feed_forward_norm", "norm"), ("feed_forward", "feed_forward"),
+              ("feed_forward_post_norm", "norm"))
+
+    capturable = True
+    accepts_next_norm = True
+
+    @classmethod
+    def _slots(cls, spec: PartSpec):
+        return [pair for pair in cls._SLOTS if spec.get("feed_forward") is not None or not pair[0].startswith("feed_forward")]
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
+        specs: list[TensorSpec] = []
+        for slot, category in cls._slots(spec):
+            child = spec[slot]
+            specs += part_class(category, child).tensor_specs(child, f"{prefix}.{spec[slot + '_name']}")
+        return specs
+
+    @classmethod
+    def cache_need(cls, spec: PartSpec) -> CacheNeed:
+        return part_class("mixer", spec["mixer"]).cache_need(spec["mixer"])
+
+    def __init__(self, spec, prefix, weights, runtime):
+        super().__init__(spec, prefix, weights, runtime)
+        self.feed_forward = self.feed_forward_norm = self.feed_forward_post_norm = None
+        for slot, category in self._slots(spec):
+            setattr(self, slot, build_part(category, spec[slot], f"{prefix}.{spec[slot + '_name']}", weights, runtime))
+
+    @property
+    def first_norm(self):
+        return self.mixer_norm
+
+    @staticmethod
+    def _joinable(norm, following) -> bool:
+        return following is not None and type(following) is type(norm) and following.eps == norm.eps and following.size == norm.size
+
+    def forward(self, residual, pending, ctx, cache: LayerCache, next_norm=None):
+        from .. import ops
+
+        if isinstance(pending, ops.LazyNorm) and pending.weight is self.mixer_norm.weight and pending.prepared is not None:
+            x = pending.prepared[0]   # the block before left this block's first norm finished
+        else:
+            x = self.mixer_norm.forward(residual, None if isinstance(pending, ops.LazyNorm) else pending)
+        branch = self.mixer.forward(x, ctx, cache)
+        last = self.mixer_post_norm
+        if self.feed_forward is not None:
+            x = self.mixer_post_norm.join(residual, branch, self.feed_forward_norm)
+            branch = self.feed_forward.forward(x, ctx)
+            last = self.feed_forward_post_norm
+        if self._joinable(last, next_norm):
+            ready = last.join(residual, branch, next_norm)
+            handle = ops.LazyNorm(residual, next_norm.weight, next_norm.eps, None, lambda: ready)
+            handle.prepared = (ready,)
+            return residual, handle
+        last.join(residual, branch, None)
+        return residual, None
+
+
+class StreamInputMixBlock(Block):
+    """x -> W [x ; x0]: the stream and the embedding's output x0 (the token's table row times a constant), side by side, through one
+    product that gives the new stream (what a model does before each pass of a run of layers that it repeats).  It keeps nothing
+    between steps and is no layer of its own in a trace.  The embedding's output is made again from the step's token ids.
+
+    params: ``tensor`` (W's full name, [size, 2 size], the stream's columns first), ``size``, ``table`` (the embedding table's name),
+    ``vocab_size``, ``scale`` (the embedding's constant), ``turn`` (which of the block's two output buffers this run writes: runs that
+    follow one another alternate)."""
+
+    capturable = True
+    traced = False
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
+        size = spec["size"]
+        return [TensorSpec(spec["tensor"], (size, 2 * size), std=(2 * size) ** -0.5), TensorSpec(spec["table"], (spec["vocab_size"], size), std=1.0)]
+
+    def __init__(self, spec, prefix, weights, runtime):
+        super().__init__(spec, prefix, weights, runtime)
+        self.size, self.scale, self.turn = int(spec["size"]), float(spec.get("scale", 1.0)), int(spec.get("turn", 0)) % 2
+        self.weight = weights.get(spec["tensor"], runtime.dtype).contiguous()
+        self.table = weights.get(spec["table"], runtime.dtype).contiguous()
+
+    def forward(self, residual, pending, ctx, cache: LayerCache):
+        from .. import ops
+
+        if pending is not None:
+            ops.add_(residual, pending)
+        ws, rows = self.runtime.workspace, residual.shape[0]
+        both = ws.get("stream_and_input", rows, 2 * self.size, self.runtime.dtype)
+        ops.stream_with_embedding(residual, self.table, ctx.token_ids, self.scale, both)
+        mixed = ws.get(f"stream_mixed_{self.turn}", rows, self.size, torch.float32)
+        ops.linear(both, self.weight, mixed)
+        return mixed, None
+
+
 register_part("block", "pre_norm_residual", PreNormResidualBlock)
+register_part("block", "sandwich_norm", SandwichNormBlock)
+register_part("block", "stream_input_mix", StreamInputMixBlock)
 register_part("block", "stream_vector", StreamVectorBlock)

@@ -1,4 +1,4 @@
-"""RMSNorm, with the residual add fused in front of it."""
+"""RMSNorm, with the residual add fused in front of it; and the layer norm without a bias."""
 from __future__ import annotations
 
 import torch
@@ -52,4 +52,46 @@ class RMSNorm(Norm):
         return out
 
 
+class LayerNorm(Norm):
+    """y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * weight: a layer norm with a weight and no bias.
+
+    params: ``size``, ``eps``, optional ``suffix`` (what follows the prefix in the tensor's name, ".weight" unless given).
+    tensors: ``<prefix><suffix> [size]``.  Mean, variance, scale and the residual sum are 32-bit in both precisions; the weight is held
+    in 32-bit.  ``forward`` adds ``delta`` into the stream first, as the RMS norm does; ``join`` is what a block calls that normalises a
+    branch before it joins the stream: ``residual += self(y)``, and in the same kernel the next norm of the stream if one is named.
+    """
+
+    capturable = True
+    supports_lazy = False
+    centred = True
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
+        return [TensorSpec(f"{prefix}{spec.get('suffix', '.weight')}", (spec["size"],), init="norm", std=0.1)]
+
+    def __init__(self, spec, prefix, weights, runtime):
+        super().__init__(spec, prefix, weights, runtime)
+        self.size = int(spec["size"])
+        self.eps = float(spec["eps"])
+        self.weight = weights.get(f"{prefix}{spec.get('suffix', '.weight')}", torch.float32).contiguous()
+
+    def forward(self, residual, delta=None, rows=None, lazy: bool = False):
+        if delta is not None:
+            ops.add_(residual, delta)
+        count = residual.shape[0] if rows is None else rows.shape[0]
+        out = self.runtime.workspace.get("normed" if rows is None else "normed_rows", count, self.size, self.runtime.dtype)
+        ops.branch_norm(residual, None, None, self.weight, out, self.eps, self.centred, rows)
+        return out
+
+    def join(self, residual, branch, following: "LayerNorm | None" = None):
+        """``residual += self(branch)``; with ``following`` (a norm of this kind and eps) also returns ``following(residual)``, one kernel."""
+        if following is None:
+            ops.branch_norm(residual, branch, self.weight, None, None, self.eps, self.centred)
+            return None
+        out = self.runtime.workspace.get("normed", residual.shape[0], self.size, self.runtime.dtype)
+        ops.branch_norm(residual, branch, self.weight, following.weight, out, self.eps, self.centred)
+        return out
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "layernorm", LayerNorm)
