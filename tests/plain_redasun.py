@@ -40,25 +40,20 @@ def differential_lambda(tensors, prefix, diff):
     return float(torch.exp((t["lq1"] * t["lk1"]).sum()) - torch.exp((t["lq2"] * t["lk2"]).sum()) + diff)
 
 
-def differential_attention(h, tensors, prefix, sizes, eps, positions=None):
-    """h [T, width] -> [T, width].  Two softmax maps per head over the same values; map 1 minus lambda times map 2."""
-    dtype = h.dtype
-    T = h.shape[0]
-    H, G, d, dv = sizes["heads"], sizes["kv_heads"], sizes["dim"], sizes["vdim"]
+def two_map_heads(q, k, v, positions, sizes, eps, lam, w_q_norm, w_k_norm):
+    """q [T, 2 H, d], k [T, 2 G, d], v [T, G, dv] as projected -> the heads' outputs [T, H, dv]: norm and rotation of q and k, two causal
+    softmax maps per head over the same values, map 1 minus lam times map 2, divided by its root mean square, times (1 - diff)."""
+    T = q.shape[0]
+    H, G, dv = sizes["heads"], sizes["kv_heads"], sizes["vdim"]
     diff = float(sizes["diff"])
-    w = lambda name: tensors[f"{prefix}.{name}"].to(dtype)
-    positions = torch.arange(T) if positions is None else positions
-    q = (h @ w("q").T).view(T, H * 2, d)
-    k = (h @ w("k").T).view(T, G * 2, d)
-    v = (h @ w("v").T).view(T, G, dv)
-    q = rms(q, eps) * w("q.norm")
-    k = rms(k, eps) * w("k.norm")
-    rot = sizes["rot"]
-    q = rotate_front(q, positions, rot["dims"], rot["base"])
-    k = rotate_front(k, positions, rot["dims"], rot["base"])
-    lam = differential_lambda(tensors, prefix, diff)
+    q = rms(q, eps) * w_q_norm
+    k = rms(k, eps) * w_k_norm
+    rot = sizes.get("rot") or {"dims": 0, "base": 1.0}
+    if rot["dims"]:
+        q = rotate_front(q, positions, rot["dims"], rot["base"])
+        k = rotate_front(k, positions, rot["dims"], rot["base"])
     visible = positions[:, None] >= positions[None, :]
-    out = torch.empty(T, H, dv, dtype=dtype)
+    out = torch.empty(T, H, dv, dtype=q.dtype)
     for head in range(H):
         g = head // (H // G)
         maps = []
@@ -68,7 +63,22 @@ def differential_attention(h, tensors, prefix, sizes, eps, positions=None):
             maps.append(torch.softmax(score, dim=-1) @ v[:, g])
         o = maps[0] - lam * maps[1]
         out[:, head] = rms(o, eps) * (1.0 - diff)
-    return out.reshape(T, H * dv) @ w("o").T
+    return out
+
+
+def differential_attention(h, tensors, prefix, sizes, eps, positions=None):
+    """h [T, width] -> [T, width]."""
+    dtype = h.dtype
+    T = h.shape[0]
+    H, G, d, dv = sizes["heads"], sizes["kv_heads"], sizes["dim"], sizes["vdim"]
+    w = lambda name: tensors[f"{prefix}.{name}"].to(dtype)
+    positions = torch.arange(T) if positions is None else positions
+    q = (h @ w("q").T).view(T, H * 2, d)
+    k = (h @ w("k").T).view(T, G * 2, d)
+    v = (h @ w("v").T).view(T, G, dv)
+    lam = differential_lambda(tensors, prefix, float(sizes["diff"]))
+    heads = two_map_heads(q, k, v, positions, sizes, eps, lam, w("q.norm"), w("k.norm"))
+    return heads.reshape(T, H * dv) @ w("o").T
 
 
 def gated_ff(h, tensors, prefix, act):

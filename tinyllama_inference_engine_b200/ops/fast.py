@@ -859,8 +859,40 @@ def named_scratch(device: torch.device, name: str, elements: int, dtype: torch.d
 
 
 # --- differential attention on the tensor cores ---------------------------------------------------
+use_diff_prefill = True
+DIFF_PREFILL_MIN_ROWS = 8    # a step whose longest entry has fewer rows stays on the general kernel, which cuts a row's keys into runs
+
+
+def diff_prefill_library(dim: int, vdim: int):
+    """The kernel set of one (key width, value width): compiled when a model of these sizes first runs a prompt portion."""
+    return load_library(f"tlie_attn_diff_k{dim}_v{vdim}", ["attention_diff_prefill.cu"], {"KEY_DIM": dim, "VALUE_DIM": vdim})
+
+
 def diff_prefill_takes(batch, rows, page_size: int, dim: int, vdim: int) -> bool:
-    return False
+    """Whether a step's differential attention runs on the tensor-core kernel: bfloat16, a prompt portion among the entries, widths
+    that are multiples of 16, and a tile that fits shared memory (the kernel set says how many rows its tile has: 0 = none)."""
+    if not use_diff_prefill or batch is None or batch.max_q_len < DIFF_PREFILL_MIN_ROWS or rows.dtype != torch.bfloat16:
+        return False
+    if dim % 16 or vdim % 16 or page_size % 16 or rows.shape[1] % 8 or batch.num_seqs > 65535:
+        return False
+    if ((2 * dim + 8) * 16 + 2 * (2 * 64 * (dim + 8) + 64 * (vdim + 8))) * 2 > 227 * 1024:
+        return False   # not even 16 rows of queries fit beside two stages of keys and values
+    return diff_prefill_library(dim, vdim).tlie_diff_prefill_tile_rows() > 0
+
+
+def diff_prefill(rows, batch, block_table, planes, out, heads: int, kv_heads: int, dim: int, vdim: int, page_size: int, scale: float, lam: float, eps: float,
+                 out_scale: float) -> None:
+    """Differential attention for a step that carries prompt portions (csrc/attention_diff_prefill.cu).  ``planes``: (key plane, its page
+    stride in elements, value plane, its page stride)."""
+    ops = _ops()
+    k_pages, k_stride, v_pages, v_stride = planes
+    ops._check(
+        diff_prefill_library(dim, vdim).tlie_diff_prefill(
+            ops._ptr(rows), c_int(rows.shape[1]), ops._ptr(k_pages), c_longlong(k_stride), ops._ptr(v_pages), c_longlong(v_stride), ops._i32(batch.seq_starts, "seq_starts"),
+            ops._i32(batch.first_positions, "first_positions"), ops._i32(block_table, "block_table"), c_int(block_table.shape[1]), ops._ptr(out), c_int(rows.shape[0]),
+            c_int(batch.num_seqs), c_int(batch.max_q_len), c_int(heads), c_int(kv_heads), c_int(page_size), c_float(scale), c_float(lam), c_float(eps), c_float(out_scale),
+            ops._stream()),
+        "diff_prefill")
 
 
 # --- routed experts on the tensor cores -------------------------------------------------------------
