@@ -400,6 +400,30 @@ def zirutar_config(size: dict, extra: dict) -> dict:
             "logit_scale": 1.0, "token_side": {"dim": extra["side"]}, "layers": layers}
 
 
+# `--designs redasun`: Redasun (differential attention with normalised, partly rotated queries and keys; layer norms before and after
+# every sublayer; gated feed-forwards with gelu, every second layer a mixture of experts with a shared expert) beside the Llama decoder, the
+# closest of the engine's designs (rotary grouped-query attention and a gated feed-forward), at equal width, layer count and vocabulary,
+# as many query and key vectors per token (two per head here) and as wide a feed-forward per token (the chosen experts' widths add up to it).
+REDASUN_SIZES = {
+    "w2048": dict(heads=16, kv_heads=2, dim=64, vdim=128, rot=32, experts=32, top=4, groups=(8, 4), expert_ff=1408, shared_ff=1408),
+    "w4096": dict(heads=16, kv_heads=4, dim=128, vdim=128, rot=64, experts=32, top=4, groups=(8, 4), expert_ff=3584, shared_ff=3584),
+}
+
+
+def redasun_config(size: dict, extra: dict) -> dict:
+    layers = []
+    for index in range(size["layers"]):
+        mixer = {"heads": extra["heads"], "kv_heads": extra["kv_heads"], "dim": extra["dim"], "vdim": extra["vdim"], "scale": extra["dim"] ** -0.5, "diff": 0.5,
+                 "rot": {"base": 10000.0, "dims": extra["rot"]}}
+        if index % 2 == 0:
+            mlp = {"kind": "dense", "ff": size["ff"]}
+        else:
+            mlp = {"kind": "moe", "expert": {"ff": extra["expert_ff"]}, "shared": {"ff": extra["shared_ff"]},
+                   "router": {"experts": extra["experts"], "top": extra["top"], "scale": 2.0, "groups": {"count": extra["groups"][0], "keep": extra["groups"][1]}}}
+        layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Redasun", "vocab": size["vocab"], "width": size["width"], "norm": {"eps": 1e-5}, "embedding": {"scale": size["width"] ** 0.5}, "layers": layers}
+
+
 def run_designs(args) -> dict:
     import numpy as np
     import torch
@@ -609,24 +633,112 @@ def run_designs(args) -> dict:
                                          "like_frac": scan_moved / (scan_ms / 1e3) / 1e9 / peak["hbm_gbs"]}
         return out
 
+    def redasun_kernel_numbers(size: dict, extra: dict) -> dict:
+        """Redasun's own kernels alone against their rooflines, beside the Llama path's like kernels: its attention at as many query and key
+        vectors of the same width, its gated feed-forward's products at the width the chosen experts add up to."""
+        H, G, D, VD = extra["heads"], extra["kv_heads"], extra["dim"], extra["vdim"]
+        LH, LG = 2 * H, 2 * G                         # the Llama path's heads: as many query and key vectors of width D
+        E, top, F, W = extra["experts"], extra["top"], extra["expert_ff"], size["width"]
+        page, bf16 = 64, torch.bfloat16
+        out = {}
+        pages_needed = -(-(context + 1) // page) * batch + -(-prompt_tokens // page)
+        planes = (torch.randn(pages_needed, 2 * G, page, D, device=device).to(bf16), torch.randn(pages_needed, G, page, VD, device=device).to(bf16))
+        like_pages = torch.randn(pages_needed, 2, LG, page, D, device=device).to(bf16)
+        inv_freq = torch.tensor([10000.0 ** (-2.0 * i / extra["rot"]) for i in range(extra["rot"] // 2)], dtype=torch.float32, device=device)
+        ones = torch.ones(D, device=device)
+        gate_up = (torch.randn(E, 2 * F, W, device=device) * W ** -0.5).to(bf16)
+        down = (torch.randn(E, W, F, device=device) * F ** -0.5).to(bf16)
+        router = torch.randn(E, W, device=device) * W ** -0.5
+        like_gate_up = (torch.randn(2 * top * F, W, device=device) * W ** -0.5).to(bf16)
+        like_down = (torch.randn(W, top * F, device=device) * F ** -0.5).to(bf16)
+
+        def context_for(lens, firsts):
+            table_width = size["positions"] // page
+            rows, at = [], 0
+            for n, f in zip(lens, firsts):
+                count = -(-(f + n) // page)
+                rows.append(list(range(at, at + count)) + [-1] * (table_width - count))
+                at += count
+            entries = [StepEntry(i, [0] * n, []) for i, n in enumerate(lens)]
+            return pack_step(entries, list(firsts), list(range(len(lens))), [rows], device)
+
+        for name, lens, firsts in (("prefill", [prompt_tokens], [0]), ("decode", [1] * batch, [context] * batch)):
+            ctx = context_for(lens, firsts)
+            tokens = sum(lens)
+            cache = LayerCache(CacheNeed("pages"), True, None, ctx.block_tables[0], page, None, planes)
+            causal = sum(f + i + 1 for n, f in zip(lens, firsts) for i in range(n))
+            width = -(-(2 * H * D + 2 * G * D + G * VD) // 8) * 8
+            rows = torch.randn(tokens, width, device=device).to(bf16)
+            mixed = torch.empty(tokens, H * VD, dtype=bf16, device=device)
+            store_ms = timed(lambda: ops.diff_store(rows, 2 * H * D, 2 * H * D + 2 * G * D, ones, ones, 1e-5, inv_freq, extra["rot"], ctx.positions, ctx.token_seq, cache, H, G, D, VD))
+            ms = timed(lambda: ops.diff_attention(rows, ctx.positions, ctx.token_seq, cache, mixed, H, G, D, VD, D ** -0.5, 0.4, 1e-5, 0.5, batch=ctx))
+            qkv = torch.randn(tokens, (LH + 2 * LG) * D, device=device).to(bf16)
+            plain = torch.empty(tokens, LH * D, dtype=bf16, device=device)
+            like_ms = timed(lambda: ops.paged_attention(qkv, like_pages, ctx.positions, ctx.token_seq, ctx.block_tables[0], plain, LH, LG, D, page, 0, D ** -0.5, batch=ctx))
+            x = torch.randn(tokens, W, device=device).to(bf16)
+            ids = torch.empty(tokens, top, dtype=torch.int32, device=device)
+            weights = torch.empty(tokens, top, device=device)
+            route_ms = timed(lambda: ops.moe_route(x, router, None, ids, weights, extra["groups"][0], extra["groups"][1], 2.0))
+            routed = torch.empty(tokens, W, dtype=bf16, device=device)
+            experts_ms = timed(lambda: ops.moe_experts(x, gate_up, down, ids, weights, None, routed, "silu", batch=ctx))
+            act = torch.empty(tokens, top * F, dtype=bf16, device=device)
+            stream = torch.zeros(tokens, W, device=device)
+
+            def like_feed_forward():
+                ops.linear_gated(x, like_gate_up, act)
+                ops.linear_accumulate(act, like_down, stream)
+
+            like_ff_ms = timed(like_feed_forward)
+            if name == "prefill":
+                flops, like_flops = causal * H * 2 * (2.0 * D + 2.0 * VD), causal * LH * 4.0 * D
+                ff_flops = tokens * top * 3 * 2.0 * F * W
+                out["attention_prefill"] = {"ms": ms, "tflops": flops / ms / 1e9, "frac": flops / (ms / 1e3) / (peak["bf16_tflops"] * 1e12), "store_ms": store_ms,
+                                            "like_ms": like_ms, "like_tflops": like_flops / like_ms / 1e9, "like_frac": like_flops / (like_ms / 1e3) / (peak["bf16_tflops"] * 1e12)}
+                out["experts_prefill"] = {"ms": experts_ms, "route_ms": route_ms, "tflops": ff_flops / experts_ms / 1e9, "frac": ff_flops / (experts_ms / 1e3) / (peak["bf16_tflops"] * 1e12),
+                                          "like_ms": like_ff_ms, "like_tflops": ff_flops / like_ff_ms / 1e9, "like_frac": ff_flops / (like_ff_ms / 1e3) / (peak["bf16_tflops"] * 1e12)}
+            else:
+                moved, like_moved = causal * G * (2 * D + VD) * 2.0, causal * LG * 2 * D * 2.0
+                chosen = len(torch.unique(ids))
+                ff_moved, like_ff_moved = chosen * 3.0 * F * W * 2.0, top * 3.0 * F * W * 2.0
+                out["attention_decode"] = {"ms": ms, "gbs": moved / ms / 1e6, "frac": moved / (ms / 1e3) / 1e9 / peak["hbm_gbs"], "store_ms": store_ms,
+                                           "like_ms": like_ms, "like_gbs": like_moved / like_ms / 1e6, "like_frac": like_moved / (like_ms / 1e3) / 1e9 / peak["hbm_gbs"]}
+                out["experts_decode"] = {"ms": experts_ms, "route_ms": route_ms, "experts_read": chosen, "gbs": ff_moved / experts_ms / 1e6, "frac": ff_moved / (experts_ms / 1e3) / 1e9 / peak["hbm_gbs"],
+                                         "like_ms": like_ff_ms, "like_gbs": like_ff_moved / like_ff_ms / 1e6, "like_frac": like_ff_moved / (like_ff_ms / 1e3) / 1e9 / peak["hbm_gbs"]}
+            y = torch.randn(tokens, W, device=device).to(bf16)
+            normed = torch.empty(tokens, W, dtype=bf16, device=device)
+            norm_ms = timed(lambda: ops.branch_norm(stream, y, torch.ones(W, device=device), torch.ones(W, device=device), normed, 1e-5, True))
+            like_norm_ms = timed(lambda: ops.add_rmsnorm(stream, y, torch.ones(W, device=device), 1e-5, normed))
+            norm_moved = tokens * W * (2 + 4 + 4 + 2.0)
+            out[f"norms_{name}"] = {"ms": norm_ms, "gbs": norm_moved / norm_ms / 1e6, "frac": norm_moved / (norm_ms / 1e3) / 1e9 / peak["hbm_gbs"],
+                                    "like_ms": like_norm_ms, "like_gbs": norm_moved / like_norm_ms / 1e6, "like_frac": norm_moved / (like_norm_ms / 1e3) / 1e9 / peak["hbm_gbs"]}
+        return out
+
     results = {}
     which = args.designs
     with ClockSampler() as clocks:
         for key, size in DESIGN_SIZES.items():
             marutar, llama = design_configs(size)
             base = Path(tempfile.gettempdir()) / f"tlie_b200_designs_{os.getuid()}_{key}"
-            pair = (("marutar", marutar), ("llama", llama)) if which == "marutar" else (("zirutar", zirutar_config(size, ZIRUTAR_SIZES[key])), ("marutar", marutar))
+            if which == "redasun":
+                pair = (("redasun", redasun_config(size, REDASUN_SIZES[key])), ("llama", llama))
+            else:
+                pair = (("marutar", marutar), ("llama", llama)) if which == "marutar" else (("zirutar", zirutar_config(size, ZIRUTAR_SIZES[key])), ("marutar", marutar))
             folders = {}
             for name, config in pair:
                 folders[name] = base / name
                 if not (folders[name] / "model.safetensors").exists():
                     write_random_model(folders[name], config, seed=0)
             results[key] = {name: model_numbers(folders[name]) for name, _ in pair}
-            results[key]["kernels"] = kernel_numbers(size) if which == "marutar" else zirutar_kernel_numbers(size, ZIRUTAR_SIZES[key])
+            if which == "redasun":
+                results[key]["kernels"] = redasun_kernel_numbers(size, REDASUN_SIZES[key])
+            else:
+                results[key]["kernels"] = kernel_numbers(size) if which == "marutar" else zirutar_kernel_numbers(size, ZIRUTAR_SIZES[key])
             results[key]["sizes"] = {k: v for k, v in size.items() if k != "pattern"} | {"pattern": "/".join(size["pattern"])}
+            if which == "redasun":
+                results[key]["sizes"] = {k: v for k, v in size.items() if k in ("width", "ff", "vocab", "layers")} | {k: (list(v) if isinstance(v, tuple) else v) for k, v in REDASUN_SIZES[key].items()}
             if which == "zirutar":
                 results[key]["sizes"] |= {k: v for k, v in ZIRUTAR_SIZES[key].items() if k != "pattern"} | {"zirutar_pattern": "/".join(ZIRUTAR_SIZES[key]["pattern"])}
-    names = "Marutar beside the Llama decoder" if which == "marutar" else "Zirutar beside Marutar"
+    names = {"marutar": "Marutar beside the Llama decoder", "zirutar": "Zirutar beside Marutar", "redasun": "Redasun beside the Llama decoder"}[which]
     return {"metric": f"prompt and decode throughput of {names} at equal sizes", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
             "data": "synthetic (random weights, uniform random token ids)", "impl": "engine", "higher_is_better": True,
             "config": {"prompt_tokens": prompt_tokens, "decode_context": context, "decode_batch": batch, "decode_steps": steps, "page_size": 64, "peaks": peak_kind,
@@ -687,7 +799,7 @@ def main() -> int:
     parser.add_argument("--impl", default="engine", choices=["engine", "reference"])
     parser.add_argument("--reference-points", action="store_true", help="with --impl reference: also time batch 1 and 64 (minutes)")
     parser.add_argument("--sections", default="decode,e2e,prefill,points,mixed", help="which measurements to take (fewer for profiling runs; `mixed` adds requests of mixed length through the scheduler)")
-    parser.add_argument("--designs", nargs="?", const="marutar", default=None, choices=["marutar", "zirutar"],
+    parser.add_argument("--designs", nargs="?", const="marutar", default=None, choices=["marutar", "zirutar", "redasun"],
                         help="instead of the headline workload: another design beside the closest existing one at equal sizes (prompt and decode throughput through "
                              "the engine, and the design's own kernels against their rooflines): Marutar beside the Llama decoder (the default), or Zirutar beside Marutar")
     args = parser.parse_args()

@@ -82,31 +82,9 @@ __device__ __forceinline__ int warp_argmax(const float* values, int n, int lane,
 
 constexpr int kRouteWarps = 4;
 
-// a warp per token; shared memory per warp: s [experts], choice [experts], group scores [groups]
-template <typename T>
-__global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router, const float* __restrict__ correction,
-                                                                     int* __restrict__ ids, float* __restrict__ weights, int tokens, int width, int experts,
-                                                                     int groups, int keep, int top, float route_scale) {
-  extern __shared__ float route_smem[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * kRouteWarps + warp;
-  if (t >= tokens) return;
-  float* s = route_smem + (size_t)warp * (2 * experts + groups);
-  float* choice = s + experts;
-  float* group_score = choice + experts;
-  const T* row = x + (size_t)t * width;
-  for (int e = 0; e < experts; ++e) {
-    const float* w = router + (size_t)e * width;
-    float sum = 0.0f;
-    for (int d = lane; d < width; d += 32) sum = fmaf(w[d], to_float(row[d]), sum);
-    sum = warp_sum(sum);
-    if (lane == 0) {
-      const float score = 1.0f / (1.0f + expf(-sum));
-      s[e] = score;
-      choice[e] = score + (correction != nullptr ? correction[e] : 0.0f);
-    }
-  }
-  __syncwarp();
+// One warp chooses a token's experts from s [experts] and choice [experts] (shared memory, written before); group_score [groups] is scratch.
+__device__ __forceinline__ void route_select(float* s, float* choice, float* group_score, int* __restrict__ ids, float* __restrict__ weights, int t, int lane,
+                                             int experts, int groups, int keep, int top, float route_scale) {
   const int per = experts / groups;
   if (groups > 1 && keep < groups) {
     for (int g = lane; g < groups; g += 32) {
@@ -167,6 +145,93 @@ __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(const T* __
   for (int k = lane; k < top; k += 32) weights[(size_t)t * top + k] *= factor;
 }
 
+// The general form: a warp per token; shared memory per warp: s [experts], choice [experts], group scores [groups]
+template <typename T>
+__global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router, const float* __restrict__ correction,
+                                                                     int* __restrict__ ids, float* __restrict__ weights, int tokens, int width, int experts,
+                                                                     int groups, int keep, int top, float route_scale) {
+  extern __shared__ float route_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * kRouteWarps + warp;
+  if (t >= tokens) return;
+  float* s = route_smem + (size_t)warp * (2 * experts + groups);
+  float* choice = s + experts;
+  float* group_score = choice + experts;
+  const T* row = x + (size_t)t * width;
+  for (int e = 0; e < experts; ++e) {
+    const float* w = router + (size_t)e * width;
+    float sum = 0.0f;
+    for (int d = lane; d < width; d += 32) sum = fmaf(w[d], to_float(row[d]), sum);
+    sum = warp_sum(sum);
+    if (lane == 0) {
+      const float score = 1.0f / (1.0f + expf(-sum));
+      s[e] = score;
+      choice[e] = score + (correction != nullptr ? correction[e] : 0.0f);
+    }
+  }
+  __syncwarp();
+  route_select(s, choice, group_score, ids, weights, t, lane, experts, groups, keep, top, route_scale);
+}
+
+constexpr int kRouteTiledWarps = 8;
+
+// Rows of a multiple of 4 numbers: a CTA of eight warps per TOK tokens.  The tokens' rows wait in shared memory as 32-bit numbers; a warp
+// takes every eighth expert and reads its row of the router once for all TOK tokens, 16 bytes a lane at a time, so that the router
+// is read tokens / TOK times (out of L2) and a step of few tokens spreads over experts as well as tokens.  A token's sum runs over
+// the columns in the same order whatever TOK is and whoever shares the CTA.  Then warp i chooses for token i as above.
+// Shared memory: x [TOK][width], then per token s [experts], choice [experts], group scores [groups].
+template <typename T, int TOK>
+__global__ void __launch_bounds__(kRouteTiledWarps * 32) moe_route_tiled_kernel(const T* __restrict__ x, const float* __restrict__ router,
+                                                                                const float* __restrict__ correction, int* __restrict__ ids,
+                                                                                float* __restrict__ weights, int tokens, int width, int experts, int groups, int keep,
+                                                                                int top, float route_scale) {
+  extern __shared__ __align__(16) float route_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t0 = blockIdx.x * TOK;
+  float* xs = route_smem;
+  float* tables = xs + (size_t)TOK * width;
+  const int per_token = 2 * experts + groups;
+  for (int i = threadIdx.x; i < TOK * width; i += blockDim.x) {
+    const int t = t0 + i / width;
+    xs[i] = t < tokens ? to_float(x[(size_t)t * width + i % width]) : 0.0f;
+  }
+  __syncthreads();
+  for (int e = warp; e < experts; e += kRouteTiledWarps) {
+    const float* w = router + (size_t)e * width;
+    float sum[TOK];
+#pragma unroll
+    for (int i = 0; i < TOK; ++i) sum[i] = 0.0f;
+#pragma unroll 4
+    for (int d = lane * 4; d < width; d += 128) {
+      const float4 a = *reinterpret_cast<const float4*>(w + d);
+#pragma unroll
+      for (int i = 0; i < TOK; ++i) {
+        const float4 b = *reinterpret_cast<const float4*>(xs + (size_t)i * width + d);
+        sum[i] = fmaf(a.x, b.x, sum[i]);
+        sum[i] = fmaf(a.y, b.y, sum[i]);
+        sum[i] = fmaf(a.z, b.z, sum[i]);
+        sum[i] = fmaf(a.w, b.w, sum[i]);
+      }
+    }
+    const float shift = correction != nullptr ? correction[e] : 0.0f;
+#pragma unroll
+    for (int i = 0; i < TOK; ++i) {
+      const float z = warp_sum(sum[i]);
+      if (lane == 0) {
+        const float score = 1.0f / (1.0f + expf(-z));
+        tables[(size_t)i * per_token + e] = score;
+        tables[(size_t)i * per_token + experts + e] = score + shift;
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = warp; i < TOK; i += kRouteTiledWarps) {
+    if (t0 + i >= tokens) break;
+    float* s = tables + (size_t)i * per_token;
+    route_select(s, s + experts, s + 2 * experts, ids, weights, t0 + i, lane, experts, groups, keep, top, route_scale);
+  }
+}
+
 constexpr int kMoeWarps = 8;
 constexpr int kGateUpOutputs = 32;   // outputs of one CTA of the direct first half
 constexpr int kDownOutputs = 32;
@@ -224,7 +289,31 @@ TLIE_EXPORT int tlie_moe_route(int dtype, const void* x, const float* router, co
   if (tokens <= 0) return 0;
   if (experts <= 0 || groups <= 0 || experts % groups != 0 || keep <= 0 || keep > groups || top <= 0 || top > keep * (experts / groups))
     return (int)cudaErrorInvalidValue;
-  const size_t smem = (size_t)kRouteWarps * (2 * experts + groups) * sizeof(float);
+  const size_t tables = (size_t)(2 * experts + groups) * sizeof(float);
+  if (width % 4 == 0 && (reinterpret_cast<uintptr_t>(router) & 15) == 0) {
+    // few tokens: a CTA each, so that the step spreads over the SMs; many: four share a CTA and a reading of the router
+    const int tok = tokens >= 4 * 2 * device_sm_count() ? 4 : 1;
+    const size_t tiled = (size_t)tok * ((size_t)width * sizeof(float) + tables);
+    if (tiled <= 200 * 1024) {
+      const int blocks = (tokens + tok - 1) / tok;
+      cudaError_t e = cudaSuccess;
+#define TLIE_ROUTE_TILED(T, TOK)                                                                                                                          \
+  do {                                                                                                                                                    \
+    if (tiled > 48 * 1024) e = cudaFuncSetAttribute(moe_route_tiled_kernel<T, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tiled);             \
+    if (e == cudaSuccess)                                                                                                                                 \
+      moe_route_tiled_kernel<T, TOK><<<blocks, kRouteTiledWarps * 32, tiled, stream>>>((const T*)x, router, correction, ids, weights, tokens, width, experts, groups, keep, \
+                                                                                     top, route_scale);                                                  \
+  } while (0)
+      if (dtype == TLIE_F32) {
+        if (tok == 4) TLIE_ROUTE_TILED(float, 4); else TLIE_ROUTE_TILED(float, 1);
+      } else {
+        if (tok == 4) TLIE_ROUTE_TILED(__nv_bfloat16, 4); else TLIE_ROUTE_TILED(__nv_bfloat16, 1);
+      }
+#undef TLIE_ROUTE_TILED
+      return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+    }
+  }
+  const size_t smem = kRouteWarps * tables;
   if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
   const int blocks = (tokens + kRouteWarps - 1) / kRouteWarps;
   if (dtype == TLIE_F32)

@@ -23,7 +23,7 @@ RECURRENT_SOURCES = ["recurrent.cu"]              # compiled when a model with a
 MIXED_ATTENTION_SOURCES = ["attention_mixed.cu"]   # likewise for attention with a distance bias, mixed heads or an output gate
 DELTA_RULE_SOURCES = ["delta_rule.cu"]             # likewise for the gated delta rule
 DIFF_ATTENTION_SOURCES = ["attention_diff.cu"]     # likewise for differential attention
-MOE_SOURCES = ["moe.cu"]                           # likewise for a feed-forward of routed experts
+MOE_SOURCES = ["moe.cu", "moe_grouped.cu"]                           # likewise for a feed-forward of routed experts
 _F32, _BF16 = 0, 1
 launch_count = 0  # kernels of this engine launched by this process (a claim the bench reports)
 
@@ -849,7 +849,7 @@ def moe_experts(x, gate_up, down, ids, weights, shared, out, activation: str = "
         raise KernelError("moe_experts: the shared branch has the output's shape and dtype", code="invalid_shape")
     if activation not in GATE_KINDS:
         raise KernelError(f"moe_experts: no activation {activation!r}", code="invalid_argument")
-    if x.dtype == torch.bfloat16 and fast.moe_grouped_takes(tokens, top, width, ff):
+    if x.dtype == torch.bfloat16 and fast.moe_grouped_takes(tokens, top, width, ff, experts):
         fast.moe_grouped(x, gate_up, down, ids, weights, shared, out, GATE_KINDS[activation])
         return
     act = fast.mixed_scratch(x.device, tokens * top * ff, x.dtype)

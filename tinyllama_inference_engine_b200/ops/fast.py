@@ -896,5 +896,28 @@ def diff_prefill(rows, batch, block_table, planes, out, heads: int, kv_heads: in
 
 
 # --- routed experts on the tensor cores -------------------------------------------------------------
-def moe_grouped_takes(tokens: int, top: int, width: int, ff: int) -> bool:
-    return False
+use_moe_grouped = True
+MOE_GROUPED_MIN_ROWS = 17     # steps of up to 16 rows read each chosen expert's rows directly, as the other small-step products do
+MOE_GROUPED_MIN_SLOTS = 64    # (token, expert) pairs from which sorting them by expert pays
+
+
+def moe_grouped_takes(tokens: int, top: int, width: int, ff: int, experts: int) -> bool:
+    """Whether a step's routed experts run as products per expert over the sorted (token, expert) pairs (csrc/moe_grouped.cu)."""
+    return use_moe_grouped and tokens >= MOE_GROUPED_MIN_ROWS and tokens * top >= MOE_GROUPED_MIN_SLOTS and width % 8 == 0 and ff % 8 == 0 and experts <= 4096
+
+
+def moe_grouped(x, gate_up, down, ids, weights, shared, out, kind: int) -> None:
+    ops = _ops()
+    tokens, width = x.shape
+    experts, two_ff, _ = gate_up.shape
+    ff, top = two_ff // 2, ids.shape[1]
+    slots = tokens * top
+    device = x.device
+    sorted_slots = named_scratch(device, "moe_sorted", slots, torch.int32)
+    meta = named_scratch(device, "moe_tiles", 1 + 3 * (slots // 64 + experts), torch.int32)
+    act = named_scratch(device, "moe_act", slots * ff, torch.bfloat16)
+    y = named_scratch(device, "moe_by_slot", slots * width, torch.float32)
+    ops._check(ops.moe_library().tlie_moe_grouped(ops._ptr(x), ops._ptr(gate_up), ops._ptr(down), ops._ptr(ids), ops._ptr(weights), ops._ptr(shared), ops._ptr(sorted_slots),
+                                                  ops._ptr(meta), ops._ptr(act), ops._ptr(y), ops._ptr(out), c_int(tokens), c_int(width), c_int(ff), c_int(experts), c_int(top),
+                                                  c_int(kind), ops._stream()), "moe_grouped")
+    ops.launch_count += 3   # four kernels: the sort, two products per expert, the sum
