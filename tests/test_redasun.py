@@ -352,7 +352,8 @@ def test_router_kernel(tokens, experts, groups, keep, top, width):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype,atol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
-@pytest.mark.parametrize("tokens,experts,top,width,ff,shared", [(5, 6, 2, 44, 10, True), (70, 8, 3, 64, 24, True), (300, 4, 1, 32, 16, False), (130, 16, 4, 128, 48, True), (1, 3, 3, 24, 8, False)])
+@pytest.mark.parametrize("tokens,experts,top,width,ff,shared", [(5, 6, 2, 44, 10, True), (70, 8, 3, 64, 24, True), (300, 4, 1, 32, 16, False), (130, 16, 4, 128, 48, True), (1, 3, 3, 24, 8, False),
+                                                                (300, 4, 1, 64, 72, False), (700, 6, 3, 136, 200, True)])   # enough rows per expert for tiles of 128 rows on tcgen05
 def test_expert_kernels(dtype, atol, tokens, experts, top, width, ff, shared):
     """The chosen experts' gated feed-forwards, weighted and summed with the shared branch: steps of few rows read the experts' rows
     directly, bfloat16 prompt portions sort by expert and use the tensor cores."""
@@ -374,6 +375,39 @@ def test_expert_kernels(dtype, atol, tokens, experts, top, width, ff, shared):
     got = torch.zeros(tokens, width, dtype=dtype, device="cuda")
     ops.moe_experts(x.cuda(), gate_up.cuda(), down.cuda(), ids.cuda(), weights.cuda(), None if branch is None else branch.cuda(), got, "silu")
     assert float((got.cpu().double() - want).abs().max()) <= atol * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("activation", ["silu", "gelu_tanh"])
+def test_expert_kernels_with_idle_and_crowded_experts(activation):
+    """Experts that no token chose, one that most chose (several row tiles) and one with a single row, at a width and an expert size that are
+    multiples of 8 only; a token's result does not depend on what else is in the step."""
+    from tinyllama_inference_engine_b200 import ops
+
+    tokens, experts, top, width, ff = 900, 7, 2, 72, 88
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(tokens, width, generator=g).bfloat16()
+    gate_up = (torch.randn(experts, 2 * ff, width, generator=g) * width ** -0.5).bfloat16()
+    down = (torch.randn(experts, width, ff, generator=g) * ff ** -0.5).bfloat16()
+    ids = torch.empty(tokens, top, dtype=torch.int32)
+    ids[:, 0] = 3                                                    # every token: the crowded expert
+    ids[:, 1] = torch.where(torch.arange(tokens) % 3 == 0, 5, 1)     # experts 0, 2, 4 and 6 stay idle
+    ids[17, 1] = 6                                                   # one row
+    weights = torch.rand(tokens, top, generator=g) + 0.1
+    z = torch.einsum("efw,tw->tef", gate_up.double(), x.double())
+    gate, up = z[:, :, :ff], z[:, :, ff:]
+    act = (gate * torch.sigmoid(gate) if activation == "silu" else plain_redasun.gelu_tanh(gate)) * up
+    y = torch.einsum("ewf,tef->tew", down.double(), act)
+    want = sum(weights[:, k, None].double() * y[torch.arange(tokens), ids[:, k].long()] for k in range(top))
+    got = torch.zeros(tokens, width, dtype=torch.bfloat16, device="cuda")
+    args = (gate_up.cuda(), down.cuda())
+    ops.moe_experts(x.cuda(), *args, ids.cuda(), weights.cuda(), None, got, activation)
+    assert int(ops.error_flag(got.device)) == 0
+    assert float((got.cpu().double() - want).abs().max()) <= 2e-2 * max(1.0, float(want.abs().max()))
+    some = torch.tensor([17, 0, 899, 450, 3])
+    alone = torch.zeros(len(some), width, dtype=torch.bfloat16, device="cuda")
+    ops.moe_experts(x[some].cuda(), *args, ids[some].cuda(), weights[some].cuda(), None, alone, activation)
+    assert float((alone.float().cpu() - got.float().cpu()[some]).abs().max()) <= 2e-2 * max(1.0, float(want.abs().max()))
 
 
 @pytest.mark.gpu

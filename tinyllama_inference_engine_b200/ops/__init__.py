@@ -23,7 +23,7 @@ RECURRENT_SOURCES = ["recurrent.cu"]              # compiled when a model with a
 MIXED_ATTENTION_SOURCES = ["attention_mixed.cu"]   # likewise for attention with a distance bias, mixed heads or an output gate
 DELTA_RULE_SOURCES = ["delta_rule.cu"]             # likewise for the gated delta rule
 DIFF_ATTENTION_SOURCES = ["attention_diff.cu"]     # likewise for differential attention
-MOE_SOURCES = ["moe.cu", "moe_grouped.cu"]                           # likewise for a feed-forward of routed experts
+MOE_SOURCES = ["moe.cu", "moe_grouped.cu", "moe_grouped_tc.cu"]   # likewise for a feed-forward of routed experts
 _F32, _BF16 = 0, 1
 launch_count = 0  # kernels of this engine launched by this process (a claim the bench reports)
 

@@ -899,6 +899,8 @@ def diff_prefill(rows, batch, block_table, planes, out, heads: int, kv_heads: in
 use_moe_grouped = True
 MOE_GROUPED_MIN_ROWS = 17     # steps of up to 16 rows read each chosen expert's rows directly, as the other small-step products do
 MOE_GROUPED_MIN_SLOTS = 64    # (token, expert) pairs from which sorting them by expert pays
+use_moe_tc = True
+MOE_TC_MIN_ROWS_PER_EXPERT = 48   # mean rows per expert from which tiles of 128 rows per expert (half of them padding, at worst) beat tiles of 64 on mma.sync
 
 
 def moe_grouped_takes(tokens: int, top: int, width: int, ff: int, experts: int) -> bool:
@@ -913,6 +915,20 @@ def moe_grouped(x, gate_up, down, ids, weights, shared, out, kind: int) -> None:
     ff, top = two_ff // 2, ids.shape[1]
     slots = tokens * top
     device = x.device
+    if use_moe_tc and slots >= MOE_TC_MIN_ROWS_PER_EXPERT * experts and width >= 64 and ff >= 64:   # a TMA box is 64 numbers of a row
+        # every expert's rows padded to tiles of 128: the TMA / tcgen05 kernel (csrc/moe_grouped_tc.cu)
+        max_rows = (slots // 128 + experts) * 128
+        row_of_slot = named_scratch(device, "moe_row_of_slot", slots, torch.int32)
+        token_of_row = named_scratch(device, "moe_token_of_row", max_rows, torch.int32)
+        meta = named_scratch(device, "moe_tile_expert", 1 + max_rows // 128, torch.int32)
+        xs = named_scratch(device, "moe_rows", max_rows * width, torch.bfloat16)
+        act = named_scratch(device, "moe_act", max_rows * ff, torch.bfloat16)
+        y = named_scratch(device, "moe_by_row", max_rows * width, torch.float32)
+        ops._check(ops.moe_library().tlie_moe_grouped_tc(ops._ptr(x), ops._ptr(gate_up), ops._ptr(down), ops._ptr(ids), ops._ptr(weights), ops._ptr(shared), ops._ptr(row_of_slot),
+                                                         ops._ptr(token_of_row), ops._ptr(meta), ops._ptr(xs), ops._ptr(act), ops._ptr(y), ops._ptr(out), c_int(tokens), c_int(width),
+                                                         c_int(ff), c_int(experts), c_int(top), c_int(kind), ops._ptr(tcgen05_error_flag(device)), ops._stream()), "moe_grouped_tc")
+        ops.launch_count += 4   # five kernels: the layout, the gathered rows, two products over all experts, the sum
+        return
     sorted_slots = named_scratch(device, "moe_sorted", slots, torch.int32)
     meta = named_scratch(device, "moe_tiles", 1 + 3 * (slots // 64 + experts), torch.int32)
     act = named_scratch(device, "moe_act", slots * ff, torch.bfloat16)
