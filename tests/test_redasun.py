@@ -287,17 +287,18 @@ ATTENTION_SHAPES = [(4, 2, 16, 32, 8), (2, 1, 32, 16, 32), (3, 3, 16, 16, 0), (6
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("dtype,atol", [(torch.float32, 1e-5), (torch.bfloat16, 6e-2)])    # bfloat16: q and the cached k, v are rounded, and dividing the
+@pytest.mark.parametrize("dtype,atol", [(torch.float32, 2e-5), (torch.bfloat16, 6e-2)])    # bfloat16: q and the cached k, v are rounded, and dividing the
 @pytest.mark.parametrize("heads,kv,dim,vdim,rot", ATTENTION_SHAPES)                         # difference of two maps by its root mean square amplifies that
-@pytest.mark.parametrize("with_batch", [False, True])
-def test_differential_attention_kernels(dtype, atol, heads, kv, dim, vdim, rot, with_batch):
+@pytest.mark.parametrize("with_batch,long_tail", [(False, False), (True, False), (True, True)])
+def test_differential_attention_kernels(dtype, atol, heads, kv, dim, vdim, rot, with_batch, long_tail):
     """Norm, rotation, cache write and the two maps against the plain function: every request in two steps, so that the second reads
     what the first cached through a scrambled block table; a portion from position 0, a decoded token and a portion that starts
     inside a page.  With the step's context the kernels are chosen as the engine chooses them (tensor cores for portions, a row's
-    keys cut into runs for steps of few rows); without it the general kernel runs alone."""
+    keys cut into runs for steps of few rows); without it the general kernel runs alone.  The last rows of every request form a third
+    step of few rows per entry (the kernel whose rows are a token's heads), over a few tiles of keys or over many."""
     from tinyllama_inference_engine_b200 import ops
 
-    lens, firsts, page_size = [37, 1, 18], [30, 52, 0], 16
+    lens, firsts, page_size = ([37, 1, 18], [30, 52, 0], 16) if not long_tail else ([5, 150, 9], [330, 0, 61], 16)
     rows, cache = _attention_case(dtype, heads, kv, dim, vdim, lens, firsts, page_size, seed=heads * 100 + dim)
     g = torch.Generator().manual_seed(7)
     q_weight, k_weight = 1 + 0.2 * torch.randn(dim, generator=g), 1 + 0.2 * torch.randn(dim, generator=g)
@@ -312,7 +313,9 @@ def test_differential_attention_kernels(dtype, atol, heads, kv, dim, vdim, rot, 
         q, k, v = x[:, :k_offset].view(total, 2 * heads, dim), x[:, k_offset:v_offset].view(total, 2 * kv, dim), x[:, v_offset : v_offset + kv * vdim].view(total, kv, vdim)
         want.append(plain_redasun.two_map_heads(q, k, v, torch.arange(total), sizes, eps, lam, q_weight.double(), k_weight.double()).reshape(total, heads * vdim))
     got = [torch.zeros_like(w) for w in want]
-    for pieces in ([(r, 0, f) for r, f in enumerate(firsts) if f > 0], [(r, f, n) for r, (n, f) in enumerate(zip(lens, firsts))]):
+    tails = [min(n, 3 + r) for r, n in enumerate(lens)]   # every request's last rows come as a step of few rows of their own
+    for pieces in ([(r, 0, f) for r, f in enumerate(firsts) if f > 0], [(r, f, n - t) for r, (n, f, t) in enumerate(zip(lens, firsts, tails)) if n > t],
+                   [(r, f + n - t, t) for r, (n, f, t) in enumerate(zip(lens, firsts, tails))]):
         step_rows, positions, token_seq, sub, batch, index = _step_of(rows, cache, pieces)
         ops.diff_store(step_rows, k_offset, v_offset, q_weight.cuda(), k_weight.cuda(), eps, inv_freq, rot, positions, token_seq, sub, heads, kv, dim, vdim)
         out = torch.zeros(len(index), heads * vdim, dtype=dtype, device="cuda")
@@ -320,7 +323,7 @@ def test_differential_attention_kernels(dtype, atol, heads, kv, dim, vdim, rot, 
         for (r, p), row in zip(index, out.cpu().double()):
             got[r][p] = row
     for r in range(len(rows)):
-        assert float((got[r] - want[r]).abs().max()) <= atol, r
+        assert float((got[r] - want[r]).abs().max()) <= atol * (2.5 if long_tail else 1.0), r    # hundreds of keys: longer 32-bit sums under the same division
 
 
 @pytest.mark.gpu

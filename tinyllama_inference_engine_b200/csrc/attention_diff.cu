@@ -171,31 +171,59 @@ __global__ void __launch_bounds__(512) diff_attention_kernel(const T* __restrict
     if (lane + 32 * i < vdim) part[2 + lane + 32 * i] = acc[i];
 }
 
-// grid (tokens, heads), 128 threads: a thread per value column (widths up to 256: two columns each)
+// grid (tokens, heads), 128 threads: a thread per value column (widths up to 256: two columns each).  Dynamic shared memory: 4 runs
+// floats.  The runs' maxima and sums are fetched side by side first and turned into one weight per (map, run), so that the loop over
+// the runs' weighted values is a row of independent loads: with a branch and an exponential between two loads, every run of a decoded
+// token's many cost a round trip to L2 of its own.  A run that saw no key has the sum 0, weight 0 and zeros for values.
 template <typename T>
 __global__ void __launch_bounds__(128) diff_merge_kernel(const float* __restrict__ parts, T* __restrict__ out, int runs, int heads, int vdim, float lambda, float eps,
                                                          float out_scale) {
+  extern __shared__ float merge_smem[];   // [2][runs] maxima, then [2][runs] weights (sums first)
   __shared__ float scratch[32];
+  float* top_s = merge_smem;
+  float* w_s = merge_smem + 2 * runs;
   const int t = blockIdx.x, head = blockIdx.y;
-  float o[2] = {0.0f, 0.0f};
+  const size_t step = (size_t)2 * heads * (vdim + 2);
+  const float* base = parts + ((size_t)t * runs * 2 * heads + (size_t)head * 2) * (vdim + 2);
+  for (int i = threadIdx.x; i < 2 * runs; i += blockDim.x) {
+    const int map = i / runs, r = i - map * runs;
+    const float* pair = base + r * step + (size_t)map * (vdim + 2);
+    top_s[i] = pair[0];
+    w_s[i] = pair[1];
+  }
+  __syncthreads();
+  float inv[2];
+#pragma unroll
   for (int map = 0; map < 2; ++map) {
-    const float* first = parts + ((size_t)t * runs * 2 * heads + (size_t)head * 2 + map) * (vdim + 2);
-    const size_t step = (size_t)2 * heads * (vdim + 2);
     float top = -INFINITY;
-    for (int r = 0; r < runs; ++r) top = fmaxf(top, first[r * step]);
-    float total = 0.0f, a[2] = {0.0f, 0.0f};
+    for (int r = 0; r < runs; ++r) top = fmaxf(top, top_s[map * runs + r]);
+    float total = 0.0f;
     for (int r = 0; r < runs; ++r) {
-      const float* part = first + r * step;
-      if (part[1] == 0.0f) continue;   // a run that saw no key
-      const float w = exp2f(part[0] - top);
-      total += part[1] * w;
+      const float sum = w_s[map * runs + r];
+      total += sum == 0.0f ? 0.0f : sum * exp2f(top_s[map * runs + r] - top);
+    }
+    inv[map] = 1.0f / total;
+    __syncthreads();
+    for (int i = threadIdx.x; i < runs; i += blockDim.x) {
+      const float sum = w_s[map * runs + i];
+      w_s[map * runs + i] = sum == 0.0f ? 0.0f : exp2f(top_s[map * runs + i] - top);
+    }
+  }
+  __syncthreads();
+  float o[2] = {0.0f, 0.0f};
+#pragma unroll
+  for (int map = 0; map < 2; ++map) {
+    const float* first = base + (size_t)map * (vdim + 2) + 2;
+    float a[2] = {0.0f, 0.0f};
+#pragma unroll 8
+    for (int r = 0; r < runs; ++r) {
+      const float w = w_s[map * runs + r];
 #pragma unroll
       for (int i = 0; i < 2; ++i)
-        if ((int)threadIdx.x + 128 * i < vdim) a[i] += part[2 + threadIdx.x + 128 * i] * w;
+        if ((int)threadIdx.x + 128 * i < vdim) a[i] = fmaf(first[r * step + threadIdx.x + 128 * i], w, a[i]);
     }
-    const float inv = 1.0f / total;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) o[i] = map == 0 ? a[i] * inv : o[i] - lambda * (a[i] * inv);
+    for (int i = 0; i < 2; ++i) o[i] = map == 0 ? a[i] * inv[0] : o[i] - lambda * (a[i] * inv[1]);
   }
   float squares = 0.0f;
 #pragma unroll
@@ -235,7 +263,7 @@ TLIE_EXPORT int tlie_diff_attention(int dtype, const void* rows, int row_stride,
                                     void* out, int tokens, int heads, int kv_heads, int dim, int vdim, int page_size, float scale, float lambda, float eps,
                                     float out_scale, int runs, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || dim > 32 * kDiffMaxPerLane || vdim > 32 * kDiffMaxPerLane || runs < 1 || runs > 65535)
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || dim > 32 * kDiffMaxPerLane || vdim > 32 * kDiffMaxPerLane || runs < 1 || runs > 2048)
     return (int)cudaErrorInvalidValue;
   const int group = heads / kv_heads;
   const int chunk_heads = group < 8 ? group : 8;
@@ -262,8 +290,21 @@ TLIE_EXPORT int tlie_diff_attention(int dtype, const void* rows, int row_stride,
   if (e != cudaSuccess) return (int)e;
   const dim3 merge_grid(tokens, heads);
   if (dtype == TLIE_F32)
-    diff_merge_kernel<float><<<merge_grid, 128, 0, stream>>>(parts, (float*)out, runs, heads, vdim, lambda, eps, out_scale);
+    diff_merge_kernel<float><<<merge_grid, 128, (size_t)4 * runs * sizeof(float), stream>>>(parts, (float*)out, runs, heads, vdim, lambda, eps, out_scale);
   else
-    diff_merge_kernel<__nv_bfloat16><<<merge_grid, 128, 0, stream>>>(parts, (__nv_bfloat16*)out, runs, heads, vdim, lambda, eps, out_scale);
+    diff_merge_kernel<__nv_bfloat16><<<merge_grid, 128, (size_t)4 * runs * sizeof(float), stream>>>(parts, (__nv_bfloat16*)out, runs, heads, vdim, lambda, eps, out_scale);
+  return (int)cudaGetLastError();
+}
+
+// The parts of another kernel's runs (csrc/attention_diff_prefill.cu's steps of few rows), joined as above.
+TLIE_EXPORT int tlie_diff_merge(int dtype, const float* parts, void* out, int tokens, int heads, int vdim, int runs, float lambda, float eps, float out_scale,
+                                cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (heads <= 0 || heads > 65535 || vdim > 32 * kDiffMaxPerLane || runs < 1 || runs > 2048) return (int)cudaErrorInvalidValue;
+  const dim3 merge_grid(tokens, heads);
+  if (dtype == TLIE_F32)
+    diff_merge_kernel<float><<<merge_grid, 128, (size_t)4 * runs * sizeof(float), stream>>>(parts, (float*)out, runs, heads, vdim, lambda, eps, out_scale);
+  else
+    diff_merge_kernel<__nv_bfloat16><<<merge_grid, 128, (size_t)4 * runs * sizeof(float), stream>>>(parts, (__nv_bfloat16*)out, runs, heads, vdim, lambda, eps, out_scale);
   return (int)cudaGetLastError();
 }

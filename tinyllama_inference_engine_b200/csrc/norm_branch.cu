@@ -10,6 +10,7 @@
 //
 // stream_with_embedding: out[t] = [residual[t] | table[ids[t]] * scale] rounded to out's type: the operand of a product that
 // mixes the stream with the embedding's output.
+#include <cstdint>
 #include "common.cuh"
 
 namespace tlie {
@@ -29,6 +30,81 @@ __device__ __forceinline__ void row_statistics(const float* row, int width, int 
     squares += d * d;
   }
   inv = 1.0f / sqrtf(block_sum(squares, scratch) / (float)width + eps);
+}
+
+// eight neighbours of a row at once, 16 bytes a load: a row of a few thousand numbers is then one or two loads per thread, all of them
+// in flight together, where a number per load made every pass of a step of few rows wait for memory several times over
+__device__ __forceinline__ void load8(const float* src, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+  v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* src, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(src);
+  const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(pairs[i]);
+    v[2 * i] = f.x, v[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void store8(float* dst, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* dst, const float (&v)[8]) {
+  uint4 raw;
+  __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) pairs[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(dst) = raw;
+}
+
+// The same kernel for rows whose width is a multiple of 8 (every row then starts on a 16-byte boundary): thread t takes the runs of
+// eight numbers t, t + block, ...  Which of the two kernels runs depends on the width alone, so a row's bits do not depend on the step.
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(kNormThreads) branch_norm_wide_kernel(float* __restrict__ residual, const TY* __restrict__ y, const float* __restrict__ post_weight,
+                                                                        const float* __restrict__ next_weight, TO* __restrict__ out, const int* __restrict__ rows,
+                                                                        float eps, int centred, int width) {
+  extern __shared__ __align__(16) float norm_row[];
+  __shared__ float scratch[32];
+  const int source = rows != nullptr ? rows[blockIdx.x] : blockIdx.x;
+  float* stream = residual + (size_t)source * width;
+  float mean, inv;
+  float a[8], b[8], w[8];
+  if (y != nullptr) {
+    const TY* branch = y + (size_t)source * width;
+    for (int i = threadIdx.x * 8; i < width; i += blockDim.x * 8) {
+      load8(branch + i, a);
+      store8(norm_row + i, a);
+    }
+    __syncthreads();
+    row_statistics(norm_row, width, centred, eps, scratch, mean, inv);
+    for (int i = threadIdx.x * 8; i < width; i += blockDim.x * 8) {   // a thread's own runs again
+      load8(stream + i, b);
+      load8(post_weight + i, w);
+      load8(norm_row + i, a);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) b[j] = b[j] + ((a[j] - mean) * inv) * w[j];
+      store8(stream + i, b);
+      store8(norm_row + i, b);
+    }
+  } else {
+    for (int i = threadIdx.x * 8; i < width; i += blockDim.x * 8) {
+      load8(stream + i, b);
+      store8(norm_row + i, b);
+    }
+  }
+  if (out == nullptr) return;
+  __syncthreads();
+  row_statistics(norm_row, width, centred, eps, scratch, mean, inv);
+  TO* dst = out + (size_t)blockIdx.x * width;
+  for (int i = threadIdx.x * 8; i < width; i += blockDim.x * 8) {
+    load8(next_weight + i, w);
+    load8(norm_row + i, a);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = ((a[j] - mean) * inv) * w[j];
+    store8(dst + i, a);
+  }
 }
 
 template <typename TY, typename TO>
@@ -86,6 +162,15 @@ static int launch_branch_norm(float* residual, const void* y, const float* post_
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(branch_norm_kernel<TY, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
+  }
+  const auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if (width % 8 == 0 && aligned(residual) && aligned(y) && aligned(post_weight) && aligned(next_weight) && aligned(out)) {
+    if (smem > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(branch_norm_wide_kernel<TY, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+    }
+    branch_norm_wide_kernel<TY, TO><<<count, kNormThreads, smem, stream>>>(residual, (const TY*)y, post_weight, next_weight, (TO*)out, rows, eps, centred, width);
+    return (int)cudaGetLastError();
   }
   branch_norm_kernel<TY, TO><<<count, kNormThreads, smem, stream>>>(residual, (const TY*)y, post_weight, next_weight, (TO*)out, rows, eps, centred, width);
   return (int)cudaGetLastError();

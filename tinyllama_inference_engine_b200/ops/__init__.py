@@ -804,6 +804,10 @@ def diff_attention(rows, positions, token_seq, cache, out, heads: int, kv_heads:
     if rows.dtype == torch.bfloat16 and fast.diff_prefill_takes(batch, rows, cache.page_size, dim, vdim):
         fast.diff_prefill(rows, batch, table, (k_pages, k_stride, v_pages, v_stride), out, heads, kv_heads, dim, vdim, cache.page_size, scale, lam, eps, out_scale)
         return
+    if batch is not None and fast.diff_decode_takes(rows, cache.page_size, dim, vdim):
+        fast.diff_decode(rows, positions, token_seq, table, (k_pages, k_stride, v_pages, v_stride), out, heads, kv_heads, dim, vdim, cache.page_size, scale, lam, eps,
+                         out_scale, batch.max_seq_len)
+        return
     runs = 1
     if batch is not None and tokens * kv_heads * 2 <= fast.sm_count():
         runs = max(1, min(2 * fast.sm_count() // (tokens * kv_heads), -(-batch.max_seq_len // 32), 64))   # down to one tile of 32 keys per CTA

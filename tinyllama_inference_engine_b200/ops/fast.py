@@ -895,6 +895,48 @@ def diff_prefill(rows, batch, block_table, planes, out, heads: int, kv_heads: in
         "diff_prefill")
 
 
+use_diff_decode = True
+
+
+def diff_decode_takes(rows, page_size: int, dim: int, vdim: int) -> bool:
+    """Whether a step of few rows per entry (decoded tokens, portions shorter than ``DIFF_PREFILL_MIN_ROWS``) runs its differential
+    attention on the tensor-core kernel whose rows are a token's heads: bfloat16, widths that are multiples of 16, a warp's tile of
+    keys and values within shared memory (the kernel set says how many warps a CTA has: 0 = none)."""
+    if not use_diff_decode or rows.dtype != torch.bfloat16 or dim % 16 or vdim % 16 or vdim > 256 or page_size % 16 or rows.shape[1] % 8:
+        return False
+    if (16 * (2 * dim + 8) + 2 * 64 * (dim + 8) + 64 * (vdim + 8)) * 2 > 227 * 1024:
+        return False
+    return diff_prefill_library(dim, vdim).tlie_diff_decode_warps() > 0
+
+
+def diff_decode(rows, positions, token_seq, block_table, planes, out, heads: int, kv_heads: int, dim: int, vdim: int, page_size: int, scale: float, lam: float,
+                eps: float, out_scale: float, longest: int) -> None:
+    """Differential attention for a step of few rows per entry: per token, the heads of a key/value head are the rows of the
+    products and every warp takes tiles of 64 keys of its own; the parts are joined, subtracted and normalised by the general
+    kernel set's merge.  ``longest``: the most keys any row sees, from which the CTAs along the keys are chosen."""
+    ops = _ops()
+    tokens = rows.shape[0]
+    lib = diff_prefill_library(dim, vdim)
+    chunks = -(-(heads // kv_heads) // 16)
+    tiles = max(1, -(-longest // 64))
+    # one wave: as many CTAs along the keys as are resident together (a CTA holds the queries and two stages of a tile of both maps' keys
+    # and the values); a CTA with several tiles fetches the next one under the products of this one
+    smem = (16 * (2 * dim + 8) + 2 * (2 * 64 * (dim + 8) + 64 * (vdim + 8))) * 2 + 1024
+    resident = sm_count() * max(1, min(227 * 1024 // smem, 16))
+    ctas = max(1, min(tiles, resident // max(1, tokens * kv_heads * chunks), 64))
+    runs = ctas
+    parts = mixed_scratch(rows.device, tokens * runs * 2 * heads * (vdim + 2), torch.float32)
+    k_pages, k_stride, v_pages, v_stride = planes
+    ops._check(
+        lib.tlie_diff_decode(ops._ptr(rows), c_int(rows.shape[1]), ops._ptr(k_pages), c_longlong(k_stride), ops._ptr(v_pages), c_longlong(v_stride),
+                             ops._i32(positions, "positions"), ops._i32(token_seq, "token_seq"), ops._i32(block_table, "block_table"), c_int(block_table.shape[1]),
+                             ops._ptr(parts), c_int(tokens), c_int(heads), c_int(kv_heads), c_int(page_size), c_float(scale), c_int(ctas), ops._stream()),
+        "diff_decode")
+    ops._check(ops.diff_attention_library().tlie_diff_merge(ops._code(rows), ops._ptr(parts), ops._ptr(out), c_int(tokens), c_int(heads), c_int(vdim), c_int(runs),
+                                                            c_float(lam), c_float(eps), c_float(out_scale), ops._stream()), "diff_merge")
+    ops.launch_count += 1   # two kernels
+
+
 # --- routed experts on the tensor cores -------------------------------------------------------------
 use_moe_grouped = True
 MOE_GROUPED_MIN_ROWS = 17     # steps of up to 16 rows read each chosen expert's rows directly, as the other small-step products do
