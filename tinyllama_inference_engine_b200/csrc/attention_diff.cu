@@ -36,13 +36,13 @@ __global__ void __launch_bounds__(128) diff_store_kernel(T* __restrict__ rows, i
   T* row = rows + (size_t)t * row_stride;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   if (page >= 0)
-    for (int i = threadIdx.x; i < v_heads * vdim; i += blockDim.x) {
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < v_heads * vdim; i += blockDim.x * gridDim.y) {
       const int head = i / vdim, d = i - head * vdim;
       v_pages[(size_t)page * v_page_stride + ((size_t)head * page_size + slot) * vdim + d] = row[v_offset + i];
     }
   const int half = rot_dims / 2;
   const float where = (float)pos;
-  for (int n = warp; n < q_vectors + k_vectors; n += warps) {
+  for (int n = blockIdx.y * warps + warp; n < q_vectors + k_vectors; n += warps * gridDim.y) {
     const bool is_key = n >= q_vectors;
     T* vector = is_key ? row + k_offset + (size_t)(n - q_vectors) * dim : row + (size_t)n * dim;
     const float* weight = is_key ? k_weight : q_weight;
@@ -245,12 +245,19 @@ TLIE_EXPORT int tlie_diff_store(int dtype, void* rows, int row_stride, int k_off
                                 int vdim, int page_size, int write_cache, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (dim > 32 * kDiffMaxPerLane || rot_dims < 0 || rot_dims > dim || rot_dims % 2 != 0) return (int)cudaErrorInvalidValue;
+  // a warp per vector where the step is small (every vector is a read, a reduction and a write that wait for one another: a token's
+  // vectors one after the other in four warps took 22 us for 8 tokens); a step of many tokens keeps more vectors per warp
+  const int vectors = 2 * heads + 2 * kv_heads;
+  int per_token = (vectors + 3) / 4;
+  while (per_token > 1 && (long long)tokens * per_token > 8192) per_token = (per_token + 1) / 2;
+  if (per_token > 65535) per_token = 65535;
+  const dim3 store_grid(tokens, per_token);
   if (dtype == TLIE_F32)
-    diff_store_kernel<float><<<tokens, 128, 0, stream>>>((float*)rows, row_stride, k_offset, v_offset, q_weight, k_weight, eps, inv_freq, rot_dims, positions, token_seq,
+    diff_store_kernel<float><<<store_grid, 128, 0, stream>>>((float*)rows, row_stride, k_offset, v_offset, q_weight, k_weight, eps, inv_freq, rot_dims, positions, token_seq,
                                                          block_table, table_stride, (float*)k_pages, k_page_stride, (float*)v_pages, v_page_stride, 2 * heads,
                                                          2 * kv_heads, kv_heads, dim, vdim, page_size, write_cache);
   else
-    diff_store_kernel<__nv_bfloat16><<<tokens, 128, 0, stream>>>((__nv_bfloat16*)rows, row_stride, k_offset, v_offset, q_weight, k_weight, eps, inv_freq, rot_dims,
+    diff_store_kernel<__nv_bfloat16><<<store_grid, 128, 0, stream>>>((__nv_bfloat16*)rows, row_stride, k_offset, v_offset, q_weight, k_weight, eps, inv_freq, rot_dims,
                                                                  positions, token_seq, block_table, table_stride, (__nv_bfloat16*)k_pages, k_page_stride,
                                                                  (__nv_bfloat16*)v_pages, v_page_stride, 2 * heads, 2 * kv_heads, kv_heads, dim, vdim, page_size,
                                                                  write_cache);

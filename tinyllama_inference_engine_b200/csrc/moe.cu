@@ -53,6 +53,105 @@ __device__ __forceinline__ float lane_dot(const __nv_bfloat16* w, const float* x
   }
   return sum;
 }
+// N rows against the same x at once: every pass of the loop has N independent 16-byte loads in flight per lane and reads its piece of x
+// once for all of them (a row at a time left a warp with one row's loads in flight and a chain of dependent sums behind each).  Every
+// row's sum is formed in the order lane_dot forms it, so the bits are the same.
+template <int N>
+__device__ __forceinline__ void lane_dot_n(const float* const (&w)[N], const float* x, int width, int lane, bool vector, float (&sums)[N]) {
+#pragma unroll
+  for (int r = 0; r < N; ++r) sums[r] = 0.0f;
+  if (vector) {
+    for (int d = lane * 4; d < width; d += 128) {
+      float4 a[N];
+#pragma unroll
+      for (int r = 0; r < N; ++r) a[r] = *reinterpret_cast<const float4*>(w[r] + d);
+      const float4 v = *reinterpret_cast<const float4*>(x + d);
+#pragma unroll
+      for (int r = 0; r < N; ++r) {
+        sums[r] = fmaf(a[r].x, v.x, sums[r]);
+        sums[r] = fmaf(a[r].y, v.y, sums[r]);
+        sums[r] = fmaf(a[r].z, v.z, sums[r]);
+        sums[r] = fmaf(a[r].w, v.w, sums[r]);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < N; ++r) sums[r] = lane_dot(w[r], x, width, lane, false);
+  }
+}
+template <int N>
+__device__ __forceinline__ void lane_dot_n(const __nv_bfloat16* const (&w)[N], const float* x, int width, int lane, bool vector, float (&sums)[N]) {
+#pragma unroll
+  for (int r = 0; r < N; ++r) sums[r] = 0.0f;
+  if (vector) {
+    for (int d = lane * 8; d < width; d += 256) {
+      uint4 raw[N];
+#pragma unroll
+      for (int r = 0; r < N; ++r) raw[r] = *reinterpret_cast<const uint4*>(w[r] + d);
+      const float4 v0 = *reinterpret_cast<const float4*>(x + d), v1 = *reinterpret_cast<const float4*>(x + d + 4);
+      const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+      for (int r = 0; r < N; ++r) {
+        const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw[r]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 a = __bfloat1622float2(pairs[i]);
+          sums[r] = fmaf(a.x, v[2 * i], sums[r]);
+          sums[r] = fmaf(a.y, v[2 * i + 1], sums[r]);
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < N; ++r) sums[r] = lane_dot(w[r], x, width, lane, false);
+  }
+}
+// 16 bytes of a row as 32-bit numbers
+__device__ __forceinline__ void load_piece(const float* p, float (&v)[4]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w;
+}
+__device__ __forceinline__ void load_piece(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 a = __bfloat1622float2(pairs[i]);
+    v[2 * i] = a.x, v[2 * i + 1] = a.y;
+  }
+}
+// Two outputs x K inputs: row w[o][k] against x[k], all 2 K rows' loads of a pass in flight together; sums as lane_dot forms them.
+template <int K, typename T>
+__device__ __forceinline__ void lane_dot_sides(const T* const (&w)[2][K], const float* const (&x)[K], int width, int lane, bool vector, float (&sums)[2][K]) {
+  constexpr int kPiece = 16 / (int)sizeof(T);
+#pragma unroll
+  for (int o = 0; o < 2; ++o)
+#pragma unroll
+    for (int k = 0; k < K; ++k) sums[o][k] = 0.0f;
+  if (vector) {
+    for (int d = lane * kPiece; d < width; d += 32 * kPiece) {
+      float a[2][K][kPiece];
+#pragma unroll
+      for (int o = 0; o < 2; ++o)
+#pragma unroll
+        for (int k = 0; k < K; ++k) load_piece(w[o][k] + d, a[o][k]);
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+#pragma unroll
+        for (int i = 0; i < kPiece; ++i) {
+          const float v = x[k][d + i];
+          sums[0][k] = fmaf(a[0][k][i], v, sums[0][k]);
+          sums[1][k] = fmaf(a[1][k][i], v, sums[1][k]);
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int o = 0; o < 2; ++o)
+#pragma unroll
+      for (int k = 0; k < K; ++k) sums[o][k] = lane_dot(w[o][k], x[k], width, lane, false);
+  }
+}
 template <typename T>
 __device__ __forceinline__ bool rows_are_vectors(const T* base, int width) {
   return width % (16 / (int)sizeof(T)) == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0;
@@ -173,15 +272,15 @@ __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(const T* __
   route_select(s, choice, group_score, ids, weights, t, lane, experts, groups, keep, top, route_scale);
 }
 
-constexpr int kRouteTiledWarps = 8;
+constexpr int kRouteTiledWarps = 8;    // steps of many tokens (four share a CTA); a CTA of one token has 16 warps
 
 // Rows of a multiple of 4 numbers: a CTA of eight warps per TOK tokens.  The tokens' rows wait in shared memory as 32-bit numbers; a warp
 // takes every eighth expert and reads its row of the router once for all TOK tokens, 16 bytes a lane at a time, so that the router
 // is read tokens / TOK times (out of L2) and a step of few tokens spreads over experts as well as tokens.  A token's sum runs over
 // the columns in the same order whatever TOK is and whoever shares the CTA.  Then warp i chooses for token i as above.
 // Shared memory: x [TOK][width], then per token s [experts], choice [experts], group scores [groups].
-template <typename T, int TOK>
-__global__ void __launch_bounds__(kRouteTiledWarps * 32) moe_route_tiled_kernel(const T* __restrict__ x, const float* __restrict__ router,
+template <typename T, int TOK, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) moe_route_tiled_kernel(const T* __restrict__ x, const float* __restrict__ router,
                                                                                 const float* __restrict__ correction, int* __restrict__ ids,
                                                                                 float* __restrict__ weights, int tokens, int width, int experts, int groups, int keep,
                                                                                 int top, float route_scale) {
@@ -191,41 +290,57 @@ __global__ void __launch_bounds__(kRouteTiledWarps * 32) moe_route_tiled_kernel(
   float* xs = route_smem;
   float* tables = xs + (size_t)TOK * width;
   const int per_token = 2 * experts + groups;
-  for (int i = threadIdx.x; i < TOK * width; i += blockDim.x) {
-    const int t = t0 + i / width;
-    xs[i] = t < tokens ? to_float(x[(size_t)t * width + i % width]) : 0.0f;
+#pragma unroll
+  for (int i = 0; i < TOK; ++i) {
+    const bool live = t0 + i < tokens;
+    const T* row = x + (size_t)(live ? t0 + i : t0) * width;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) xs[(size_t)i * width + d] = live ? to_float(row[d]) : 0.0f;
   }
   __syncthreads();
-  for (int e = warp; e < experts; e += kRouteTiledWarps) {
-    const float* w = router + (size_t)e * width;
-    float sum[TOK];
+  // two experts of a warp side by side and four pieces of each ahead: a row at a time with one piece in flight made a step of few
+  // tokens wait for memory once per 512 bytes of a row.  An expert past the end reads the last one again and writes nothing.
+  for (int e0 = warp; e0 < experts; e0 += 2 * WARPS) {
+    const int e1 = e0 + WARPS;
+    const float* w0 = router + (size_t)e0 * width;
+    const float* w1 = router + (size_t)min(e1, experts - 1) * width;
+    float sum[2][TOK];
 #pragma unroll
-    for (int i = 0; i < TOK; ++i) sum[i] = 0.0f;
+    for (int i = 0; i < TOK; ++i) sum[0][i] = sum[1][i] = 0.0f;
 #pragma unroll 4
     for (int d = lane * 4; d < width; d += 128) {
-      const float4 a = *reinterpret_cast<const float4*>(w + d);
+      const float4 a0 = *reinterpret_cast<const float4*>(w0 + d);
+      const float4 a1 = *reinterpret_cast<const float4*>(w1 + d);
 #pragma unroll
       for (int i = 0; i < TOK; ++i) {
         const float4 b = *reinterpret_cast<const float4*>(xs + (size_t)i * width + d);
-        sum[i] = fmaf(a.x, b.x, sum[i]);
-        sum[i] = fmaf(a.y, b.y, sum[i]);
-        sum[i] = fmaf(a.z, b.z, sum[i]);
-        sum[i] = fmaf(a.w, b.w, sum[i]);
+        sum[0][i] = fmaf(a0.x, b.x, sum[0][i]);
+        sum[0][i] = fmaf(a0.y, b.y, sum[0][i]);
+        sum[0][i] = fmaf(a0.z, b.z, sum[0][i]);
+        sum[0][i] = fmaf(a0.w, b.w, sum[0][i]);
+        sum[1][i] = fmaf(a1.x, b.x, sum[1][i]);
+        sum[1][i] = fmaf(a1.y, b.y, sum[1][i]);
+        sum[1][i] = fmaf(a1.z, b.z, sum[1][i]);
+        sum[1][i] = fmaf(a1.w, b.w, sum[1][i]);
       }
     }
-    const float shift = correction != nullptr ? correction[e] : 0.0f;
 #pragma unroll
-    for (int i = 0; i < TOK; ++i) {
-      const float z = warp_sum(sum[i]);
-      if (lane == 0) {
-        const float score = 1.0f / (1.0f + expf(-z));
-        tables[(size_t)i * per_token + e] = score;
-        tables[(size_t)i * per_token + experts + e] = score + shift;
+    for (int j = 0; j < 2; ++j) {
+      const int e = j == 0 ? e0 : e1;
+      if (e >= experts) break;
+      const float shift = correction != nullptr ? correction[e] : 0.0f;
+#pragma unroll
+      for (int i = 0; i < TOK; ++i) {
+        const float z = warp_sum(sum[j][i]);
+        if (lane == 0) {
+          const float score = 1.0f / (1.0f + expf(-z));
+          tables[(size_t)i * per_token + e] = score;
+          tables[(size_t)i * per_token + experts + e] = score + shift;
+        }
       }
     }
   }
   __syncthreads();
-  for (int i = warp; i < TOK; i += kRouteTiledWarps) {
+  for (int i = warp; i < TOK; i += WARPS) {
     if (t0 + i >= tokens) break;
     float* s = tables + (size_t)i * per_token;
     route_select(s, s + experts, s + 2 * experts, ids, weights, t0 + i, lane, experts, groups, keep, top, route_scale);
@@ -247,12 +362,26 @@ __global__ void __launch_bounds__(kMoeWarps * 32) moe_gate_up_kernel(const T* __
   __syncthreads();
   const T* expert = gate_up + (size_t)ids[slot] * 2 * ff * width;
   const bool vector = rows_are_vectors(expert, width);
-  for (int i = warp; i < kGateUpOutputs; i += kMoeWarps) {
-    const int f = blockIdx.y * kGateUpOutputs + i;
-    if (f >= ff) break;
-    const float g = warp_sum(lane_dot(expert + (size_t)f * width, moe_x, width, lane, vector));
-    const float u = warp_sum(lane_dot(expert + (size_t)(ff + f) * width, moe_x, width, lane, vector));
-    if (lane == 0) act[(size_t)slot * ff + f] = from_float<T>(moe_act(g, kind) * u);
+  // a warp's outputs (warp, warp + kMoeWarps, ...) four at a time: four gate rows and four up rows side by side.  Outputs past the end
+  // read the last row again and store nothing.
+  constexpr int kPerWarp = kGateUpOutputs / kMoeWarps;
+  static_assert(kPerWarp == 4, "four outputs per warp");
+  const T* rows[2 * kPerWarp];
+  int f[kPerWarp];
+#pragma unroll
+  for (int j = 0; j < kPerWarp; ++j) {
+    f[j] = blockIdx.y * kGateUpOutputs + warp + j * kMoeWarps;
+    const int row = min(f[j], ff - 1);
+    rows[2 * j] = expert + (size_t)row * width;
+    rows[2 * j + 1] = expert + (size_t)(ff + row) * width;
+  }
+  float sums[2 * kPerWarp];
+  lane_dot_n<2 * kPerWarp>(rows, moe_x, width, lane, vector, sums);
+#pragma unroll
+  for (int j = 0; j < kPerWarp; ++j) {
+    const float g = warp_sum(sums[2 * j]);
+    const float u = warp_sum(sums[2 * j + 1]);
+    if (lane == 0 && f[j] < ff) act[(size_t)slot * ff + f[j]] = from_float<T>(moe_act(g, kind) * u);
   }
 }
 
@@ -267,16 +396,44 @@ __global__ void __launch_bounds__(kMoeWarps * 32) moe_down_kernel(const T* __res
   for (int i = threadIdx.x; i < top * ff; i += blockDim.x) moe_act_rows[i] = to_float(act[(size_t)t * top * ff + i]);
   __syncthreads();
   const bool vector = rows_are_vectors(down, ff);
-  for (int i = warp; i < kDownOutputs; i += kMoeWarps) {
-    const int n = blockIdx.y * kDownOutputs + i;
-    if (n >= width) break;
-    float total = 0.0f;
-    for (int k = 0; k < top; ++k) {
-      const T* expert = down + ((size_t)ids[(size_t)t * top + k] * width + n) * ff;
-      total += weights[(size_t)t * top + k] * warp_sum(lane_dot(expert, moe_act_rows + (size_t)k * ff, ff, lane, vector));
+  // two of a warp's outputs at a time, each with four chosen experts' rows side by side (eight rows in flight); experts past ``top``
+  // read the last one's row again and are left out of the sum.  A token's experts are added in the order they were chosen.
+  constexpr int kSide = 4;
+  for (int i = warp; i < kDownOutputs; i += 2 * kMoeWarps) {
+    int n[2];
+    n[0] = blockIdx.y * kDownOutputs + i;
+    n[1] = n[0] + kMoeWarps;
+    if (n[0] >= width) break;
+    float total[2] = {0.0f, 0.0f};
+    for (int k0 = 0; k0 < top; k0 += kSide) {
+      const T* rows[2][kSide];
+      const float* inputs[kSide];
+#pragma unroll
+      for (int j = 0; j < kSide; ++j) {
+        const int k = min(k0 + j, top - 1);
+        const size_t expert = (size_t)ids[(size_t)t * top + k] * width;
+        inputs[j] = moe_act_rows + (size_t)k * ff;
+#pragma unroll
+        for (int o = 0; o < 2; ++o) rows[o][j] = down + (expert + min(n[o], width - 1)) * ff;
+      }
+      float sums[2][kSide];
+      lane_dot_sides<kSide>(rows, inputs, ff, lane, vector, sums);
+#pragma unroll
+      for (int j = 0; j < kSide; ++j) {
+#pragma unroll
+        for (int o = 0; o < 2; ++o) {
+          const float dot = warp_sum(sums[o][j]);
+          if (k0 + j < top) total[o] += weights[(size_t)t * top + k0 + j] * dot;
+        }
+      }
     }
-    if (shared != nullptr) total += to_float(shared[(size_t)t * width + n]);
-    if (lane == 0) out[(size_t)t * width + n] = from_float<T>(total);
+#pragma unroll
+    for (int o = 0; o < 2; ++o) {
+      if (n[o] >= width) continue;
+      float value = total[o];
+      if (shared != nullptr) value += to_float(shared[(size_t)t * width + n[o]]);
+      if (lane == 0) out[(size_t)t * width + n[o]] = from_float<T>(value);
+    }
   }
 }
 
@@ -299,9 +456,9 @@ TLIE_EXPORT int tlie_moe_route(int dtype, const void* x, const float* router, co
       cudaError_t e = cudaSuccess;
 #define TLIE_ROUTE_TILED(T, TOK)                                                                                                                          \
   do {                                                                                                                                                    \
-    if (tiled > 48 * 1024) e = cudaFuncSetAttribute(moe_route_tiled_kernel<T, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tiled);             \
+    if (tiled > 48 * 1024) e = cudaFuncSetAttribute(moe_route_tiled_kernel<T, TOK, (TOK == 1 ? 16 : kRouteTiledWarps)>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tiled);             \
     if (e == cudaSuccess)                                                                                                                                 \
-      moe_route_tiled_kernel<T, TOK><<<blocks, kRouteTiledWarps * 32, tiled, stream>>>((const T*)x, router, correction, ids, weights, tokens, width, experts, groups, keep, \
+      moe_route_tiled_kernel<T, TOK, (TOK == 1 ? 16 : kRouteTiledWarps)><<<blocks, (TOK == 1 ? 16 : kRouteTiledWarps) * 32, tiled, stream>>>((const T*)x, router, correction, ids, weights, tokens, width, experts, groups, keep, \
                                                                                      top, route_scale);                                                  \
   } while (0)
       if (dtype == TLIE_F32) {

@@ -27,6 +27,7 @@ def sm_count() -> int:
 
 DEFAULT_HEAD_DIMS = (64, 128)
 DEFAULT_MIXED_PREFILL_SETS = ((64, 64, 4), (128, 128, 8))   # (key width, value width, key heads per folded query) built ahead; others on first use
+DEFAULT_DIFF_SETS = ((64, 128), (128, 128))   # (key width per map, value width) of differential attention built ahead; others on first use
 _scratch: dict[torch.device, list[torch.Tensor]] = {}
 
 
@@ -44,6 +45,8 @@ def build_all() -> list:
         built.append(build_library(f"tlie_attn_mixed_decode_k{key_dim}_v{value_dim}_g{parts}", ["attention_mixed_decode.cu"],
                                    {"KEY_DIM": key_dim, "VALUE_DIM": value_dim, "KV_HEADS": parts}))
     built.append(build_library("tlie_attn_latent_k576_v512", ["attention_latent_prefill.cu"], {"KEY_DIM": 576, "VALUE_DIM": 512}))   # other widths on first use
+    for key_dim, value_dim in DEFAULT_DIFF_SETS:
+        built.append(build_library(f"tlie_attn_diff_k{key_dim}_v{value_dim}", ["attention_diff_prefill.cu"], {"KEY_DIM": key_dim, "VALUE_DIM": value_dim}))
     return built
 
 
