@@ -246,7 +246,7 @@ TLIE_EXPORT int tlie_diff_store(int dtype, void* rows, int row_stride, int k_off
   if (tokens <= 0) return 0;
   if (dim > 32 * kDiffMaxPerLane || rot_dims < 0 || rot_dims > dim || rot_dims % 2 != 0) return (int)cudaErrorInvalidValue;
   // a warp per vector where the step is small (every vector is a read, a reduction and a write that wait for one another: a token's
-  // vectors one after the other in four warps took 22 us for 8 tokens); a step of many tokens keeps more vectors per warp
+  // vectors one after the other in four warps took 22 us for 8 tokens); a step of many tokens keeps more vectors per warp (more CTAs than that were measured: slower)
   const int vectors = 2 * heads + 2 * kv_heads;
   int per_token = (vectors + 3) / 4;
   while (per_token > 1 && (long long)tokens * per_token > 8192) per_token = (per_token + 1) / 2;

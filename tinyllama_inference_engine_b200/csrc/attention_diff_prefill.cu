@@ -358,8 +358,7 @@ __global__ void __launch_bounds__(kDecThreads)
         mma_bf16(s_frag[jp * 2 + 1], qa, b[2], b[3]);
       }
     }
-    float tile_max = -INFINITY;   // every row is at the token's position: one mask, but a maximum per row
-    float tile_max_r[2] = {-INFINITY, -INFINITY};
+    float tile_max_r[2] = {-INFINITY, -INFINITY};   // every row is at the token's position: one mask, but a maximum per row
 #pragma unroll
     for (int j = 0; j < kKeys / 8; ++j) {
 #pragma unroll
@@ -370,7 +369,6 @@ __global__ void __launch_bounds__(kDecThreads)
         tile_max_r[e >> 1] = fmaxf(tile_max_r[e >> 1], v);
       }
     }
-    (void)tile_max;
     float rescale[2], base[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
