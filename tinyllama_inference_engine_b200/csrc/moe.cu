@@ -152,6 +152,43 @@ __device__ __forceinline__ void lane_dot_sides(const T* const (&w)[2][K], const 
       for (int k = 0; k < K; ++k) sums[o][k] = lane_dot(w[o][k], x[k], width, lane, false);
   }
 }
+// The same for bfloat16 rows with the pieces kept as they were loaded (four registers each, not eight) until they are used: with the
+// converted pieces the kernel took 102 registers and two CTAs an SM, sixteen warps, which left the loads in flight short of what memory needs.
+template <int K>
+__device__ __forceinline__ void lane_dot_sides(const __nv_bfloat16* const (&w)[2][K], const float* const (&x)[K], int width, int lane, bool vector, float (&sums)[2][K]) {
+#pragma unroll
+  for (int o = 0; o < 2; ++o)
+#pragma unroll
+    for (int k = 0; k < K; ++k) sums[o][k] = 0.0f;
+  if (vector) {
+    for (int d = lane * 8; d < width; d += 256) {
+      uint4 raw[2][K];
+#pragma unroll
+      for (int o = 0; o < 2; ++o)
+#pragma unroll
+        for (int k = 0; k < K; ++k) raw[o][k] = *reinterpret_cast<const uint4*>(w[o][k] + d);
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const __nv_bfloat162* p0 = reinterpret_cast<const __nv_bfloat162*>(&raw[0][k]);
+        const __nv_bfloat162* p1 = reinterpret_cast<const __nv_bfloat162*>(&raw[1][k]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 a0 = __bfloat1622float2(p0[i]), a1 = __bfloat1622float2(p1[i]);
+          const float v0 = x[k][d + 2 * i], v1 = x[k][d + 2 * i + 1];
+          sums[0][k] = fmaf(a0.x, v0, sums[0][k]);
+          sums[1][k] = fmaf(a1.x, v0, sums[1][k]);
+          sums[0][k] = fmaf(a0.y, v1, sums[0][k]);
+          sums[1][k] = fmaf(a1.y, v1, sums[1][k]);
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int o = 0; o < 2; ++o)
+#pragma unroll
+      for (int k = 0; k < K; ++k) sums[o][k] = lane_dot(w[o][k], x[k], width, lane, false);
+  }
+}
 template <typename T>
 __device__ __forceinline__ bool rows_are_vectors(const T* base, int width) {
   return width % (16 / (int)sizeof(T)) == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0;
@@ -387,7 +424,7 @@ __global__ void __launch_bounds__(kMoeWarps * 32) moe_gate_up_kernel(const T* __
 
 // grid (tokens, ceil(width / 32)); out[t] = sum_k weight_k * W_down[e_k] act[t, k]  (+ shared[t])
 template <typename T>
-__global__ void __launch_bounds__(kMoeWarps * 32) moe_down_kernel(const T* __restrict__ act, const T* __restrict__ down, const int* __restrict__ ids,
+__global__ void __launch_bounds__(kMoeWarps * 32, 4) moe_down_kernel(const T* __restrict__ act, const T* __restrict__ down, const int* __restrict__ ids,
                                                                   const float* __restrict__ weights, const T* __restrict__ shared, T* __restrict__ out, int width,
                                                                   int ff, int top) {
   extern __shared__ float moe_act_rows[];   // [top][ff]
