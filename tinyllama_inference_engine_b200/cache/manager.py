@@ -90,26 +90,28 @@ class CacheManager:
         self.poison = poison_freed_pages
         self.page_groups: list[PageGroup] = []
         self.state_groups: list[StateGroup] = []
-        self.stream_group: dict[int, tuple[str, int, int]] = {}  # stream -> (kind, group index, index in group)
-        by_key: dict[tuple, list[int]] = {}
+        by_pages: dict[tuple, list[int]] = {}
+        by_state: dict[tuple, list[int]] = {}
         for stream in sorted(needs):
-            by_key.setdefault(needs[stream].group_key(), []).append(stream)
-        for key, streams in by_key.items():
-            need = needs[streams[0]]
-            if need.kind == "pages":
-                group = PageGroup(len(self.page_groups), need, streams, page_size, num_pages)
-                self.page_groups.append(group)
-            elif need.kind == "state":
-                group = StateGroup(len(self.state_groups), need, streams)
-                self.state_groups.append(group)
-            elif need.kind == "none":
-                for stream in streams:
-                    self.stream_group[stream] = ("none", 0, 0)
-                continue
-            else:
+            need = needs[stream]
+            if need.kind not in ("pages", "state", "none"):
                 raise EngineError(f"unknown cache need kind {need.kind!r}", code="invalid_argument")
+            if need.page_key() is not None:
+                by_pages.setdefault(need.page_key(), []).append(stream)
+            if need.state_key() is not None:
+                by_state.setdefault(need.state_key(), []).append(stream)
+        # stream -> {"pages": (group index, index in group), "state": (group index, index in group)}; a stream may be in both
+        self.stream_group = {stream: {} for stream in needs}
+        for streams in by_pages.values():
+            group = PageGroup(len(self.page_groups), needs[streams[0]], streams, page_size, num_pages)
+            self.page_groups.append(group)
             for position, stream in enumerate(streams):
-                self.stream_group[stream] = (need.kind, group.index, position)
+                self.stream_group[stream]["pages"] = (group.index, position)
+        for streams in by_state.values():
+            group = StateGroup(len(self.state_groups), needs[streams[0]], streams)
+            self.state_groups.append(group)
+            for position, stream in enumerate(streams):
+                self.stream_group[stream]["state"] = (group.index, position)
         self.needs = dict(needs)
         self._has_windows = any(group.need.window > 0 for group in self.page_groups)
         self.records: dict[object, RequestRecord] = {}
@@ -131,7 +133,7 @@ class CacheManager:
                 for tensor in group.tensors():
                     tensor.fill_(float("nan"))
         for group in self.state_groups:
-            shape = (len(group.streams), self.max_requests, *group.need.state_shape)
+            shape = (len(group.streams), self.max_requests, *group.need.state_key())
             group.tensor = torch.zeros(shape, dtype=torch.float32, device=self.device)
 
     def cache_bytes(self) -> int:
@@ -241,17 +243,18 @@ class CacheManager:
     def layer_caches(self, block_tables: list[torch.Tensor]) -> dict[int, LayerCache]:
         """A LayerCache per cache stream, given this step's block tables (one per page group)."""
         caches: dict[int, LayerCache] = {}
-        for stream, (kind, group_index, position) in self.stream_group.items():
-            need = self.needs[stream]
-            if kind == "pages":
+        for stream, member in self.stream_group.items():
+            cache = LayerCache(self.needs[stream], True)
+            if "pages" in member:
+                group_index, position = member["pages"]
                 group = self.page_groups[group_index]
-                caches[stream] = LayerCache(need, True, None if group.tensor is None else group.tensor[position], block_tables[group_index], self.page_size, None,
-                                            tuple(tensor[position] for tensor in group.plane_tensors))
-            elif kind == "state":
-                group = self.state_groups[group_index]
-                caches[stream] = LayerCache(need, True, None, None, 0, group.tensor[position])
-            else:
-                caches[stream] = LayerCache(need, True)
+                cache.pages = None if group.tensor is None else group.tensor[position]
+                cache.block_table, cache.page_size = block_tables[group_index], self.page_size
+                cache.plane_pages = tuple(tensor[position] for tensor in group.plane_tensors)
+            if "state" in member:
+                group_index, position = member["state"]
+                cache.state = self.state_groups[group_index].tensor[position]
+            caches[stream] = cache
         return caches
 
     # --- accounting -----------------------------------------------------------------------

@@ -47,6 +47,57 @@ __global__ void store_kv_planes_kernel(const T* __restrict__ rows, int row_strid
   }
 }
 
+// Biases, a partial rotation and the cache write for attention whose keys and values are planes of different widths.  A row of
+// ``rows`` holds the products [q: heads x key_dim | ... k at k_offset: kv_heads x key_dim | ... v at v_offset: kv_heads x value_dim].
+// Each vector gets its bias (32-bit, null: none); of every q and k head the first ``rot_dims`` columns turn, column i with column
+// i + rot_dims / 2, by position * inv_freq[i] (angle, sine and cosine in 32-bit); q is left in place, k and v go into the token's page.
+template <typename T>
+__global__ void __launch_bounds__(128) rotary_store_planes_kernel(T* __restrict__ rows, int row_stride, int k_offset, int v_offset, const float* __restrict__ q_bias,
+                                                                  const float* __restrict__ k_bias, const float* __restrict__ v_bias, const float* __restrict__ inv_freq,
+                                                                  int rot_dims, const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                                                  const int* __restrict__ block_table, int table_stride, T* __restrict__ k_pages, long long k_page_stride,
+                                                                  T* __restrict__ v_pages, long long v_page_stride, int heads, int kv_heads, int key_dim, int value_dim,
+                                                                  int page_size, int write_cache) {
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int page = write_cache ? block_table[(size_t)token_seq[t] * table_stride + pos / page_size] : -1;
+  const int slot = pos % page_size;
+  T* row = rows + (size_t)t * row_stride;
+  const int half = rot_dims / 2;
+  const int units = key_dim - half;   // per head: ``half`` pairs, then the columns that do not turn
+  for (int i = threadIdx.x; i < (heads + kv_heads) * units; i += blockDim.x) {
+    const int h = i / units, u = i - h * units;
+    const bool is_key = h >= heads;
+    const int head = is_key ? h - heads : h;
+    T* vec = row + (is_key ? k_offset : 0) + (size_t)head * key_dim;
+    const float* bias = is_key ? k_bias : q_bias;
+    T* dst = (is_key && page >= 0) ? k_pages + (size_t)page * k_page_stride + ((size_t)head * page_size + slot) * key_dim : nullptr;
+    if (u < half) {
+      float a = to_float(vec[u]), b = to_float(vec[u + half]);
+      if (bias != nullptr) a += bias[head * key_dim + u], b += bias[head * key_dim + u + half];
+      float sine, cosine;
+      sincosf((float)pos * inv_freq[u], &sine, &cosine);
+      const T first = from_float<T>(a * cosine - b * sine), second = from_float<T>(b * cosine + a * sine);
+      if (!is_key) vec[u] = first, vec[u + half] = second;
+      if (dst != nullptr) dst[u] = first, dst[u + half] = second;
+    } else {
+      const int d = u + half;
+      float a = to_float(vec[d]);
+      if (bias != nullptr) a += bias[head * key_dim + d];
+      const T value = from_float<T>(a);
+      if (!is_key) vec[d] = value;
+      if (dst != nullptr) dst[d] = value;
+    }
+  }
+  if (page < 0) return;
+  for (int i = threadIdx.x; i < kv_heads * value_dim; i += blockDim.x) {
+    const int head = i / value_dim, d = i - head * value_dim;
+    float a = to_float(row[v_offset + i]);
+    if (v_bias != nullptr) a += v_bias[i];
+    v_pages[(size_t)page * v_page_stride + ((size_t)head * page_size + slot) * value_dim + d] = from_float<T>(a);
+  }
+}
+
 // Queries and keys divided by their root mean square per head (optionally times a weight), then the cache write: the normalised
 // keys into the key plane and ``kv_heads * value_dim`` columns from ``v_offset`` into the value plane as they are (with
 // ``v_offset == k_offset`` the values are the keys before the norm).  q is normalised in place.  A warp per head.
@@ -527,6 +578,25 @@ TLIE_EXPORT int tlie_store_kv_planes(int dtype, const void* rows, int row_stride
     store_kv_planes_kernel<__nv_bfloat16><<<tokens, 128, 0, stream>>>((const __nv_bfloat16*)rows, row_stride, k_offset, v_offset, positions, token_seq,
                                                                       block_table, table_stride, (__nv_bfloat16*)k_pages, k_page_stride,
                                                                       (__nv_bfloat16*)v_pages, v_page_stride, kv_heads, key_dim, value_dim, page_size);
+  return (int)cudaGetLastError();
+}
+
+// ``q_bias`` / ``k_bias`` / ``v_bias`` null: none.  ``rot_dims`` 0 (then ``inv_freq`` may be null): nothing turns.
+TLIE_EXPORT int tlie_rotary_store_planes(int dtype, void* rows, int row_stride, int k_offset, int v_offset, const float* q_bias, const float* k_bias, const float* v_bias,
+                                         const float* inv_freq, int rot_dims, const int* positions, const int* token_seq, const int* block_table, int table_stride,
+                                         void* k_pages, long long k_page_stride, void* v_pages, long long v_page_stride, int tokens, int heads, int kv_heads, int key_dim,
+                                         int value_dim, int page_size, int write_cache, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (rot_dims < 0 || rot_dims % 2 || rot_dims > key_dim || (rot_dims > 0 && inv_freq == nullptr)) return (int)cudaErrorInvalidValue;
+  if (dtype == TLIE_F32)
+    rotary_store_planes_kernel<float><<<tokens, 128, 0, stream>>>((float*)rows, row_stride, k_offset, v_offset, q_bias, k_bias, v_bias, inv_freq, rot_dims, positions,
+                                                                  token_seq, block_table, table_stride, (float*)k_pages, k_page_stride, (float*)v_pages, v_page_stride,
+                                                                  heads, kv_heads, key_dim, value_dim, page_size, write_cache);
+  else
+    rotary_store_planes_kernel<__nv_bfloat16><<<tokens, 128, 0, stream>>>((__nv_bfloat16*)rows, row_stride, k_offset, v_offset, q_bias, k_bias, v_bias, inv_freq, rot_dims,
+                                                                          positions, token_seq, block_table, table_stride, (__nv_bfloat16*)k_pages, k_page_stride,
+                                                                          (__nv_bfloat16*)v_pages, v_page_stride, heads, kv_heads, key_dim, value_dim, page_size,
+                                                                          write_cache);
   return (int)cudaGetLastError();
 }
 

@@ -16,6 +16,11 @@
 //                    on their way (asynchronous copies into a ring of 16) while a block of four is worked on between two barriers
 //   delta_gate_norm  per (token, head): o / sqrt(mean(o^2) + eps) * weight * sigmoid(gate)
 //
+// The same recurrence without the correction (``plain``: u = beta v) serves other linear-attention mixers: with decay f, key 1 - f and
+// beta 1 it is S <- diag(f) S + (1 - f) v^T (hgrn2_prepare); with one decay per head, key B, value x, beta dt and query C it is the
+// state-space model S <- a S + dt B x^T, y = S^T C (ssd_prepare, and ssd_finish for the skip term, the gate and the grouped norm).
+// ``decay_per_head``: one decay per head (g = exp(-exp(A_log_h) softplus(a_h + dt_bias_h))), written to all the head's key channels.
+//
 // State of a request (32-bit words): for every head the matrix in the order the recurrence reads it,
 // [4 ceil(dim / 32)][vdim][8] (lane l of a column's 8 holds key channels 32 (i / 4) + 4 l + i % 4 at [i][j][l]: four neighbours per
 // 16-byte read of the staged operands), then the convolution's inputs [taps - 1][channels].  (TLIE_DELTA_LANES=16 at compile time,
@@ -40,7 +45,8 @@ __device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : lo
 // the value heads: convolution and silu, and beside them the head's beta and its dim decays.  Few rows (decoded tokens) then still
 // fill the SMs, and a thread's loads (the taps of one channel) do not wait for one another.
 template <typename T>
-__global__ void __launch_bounds__(128) delta_prepare_kernel(const T* __restrict__ rows, int row_stride, int beta_offset, const T* __restrict__ a, const float* __restrict__ taps_w,
+__global__ void __launch_bounds__(128) delta_prepare_kernel(const T* __restrict__ rows, int row_stride, int beta_offset, const T* __restrict__ a, long long a_stride,
+                                                            int decay_per_head, const float* __restrict__ taps_w,
                                                             const float* __restrict__ a_log, const float* __restrict__ dt_bias, const float* __restrict__ state,
                                                             long long state_stride, long long conv_offset, const int* __restrict__ token_seq,
                                                             const int* __restrict__ seq_starts, const int* __restrict__ state_slots, float* __restrict__ prep,
@@ -86,7 +92,8 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(const T* __restrict_
   const float rate = expf(a_log[h]);
   for (int d = threadIdx.x; d < dim; d += blockDim.x) {
     const int i = h * dim + d;
-    out[channels + heads + i] = expf(-rate * softplus_f(to_float(a[(size_t)t * heads * dim + i]) + dt_bias[i]));
+    const int from = decay_per_head ? h : i;
+    out[channels + heads + i] = expf(-rate * softplus_f(to_float(a[(size_t)t * a_stride + from]) + dt_bias[from]));
   }
 }
 
@@ -123,7 +130,7 @@ __device__ __forceinline__ void delta_wait() { asm volatile("cp.async.wait_group
 template <int R>
 __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* __restrict__ prep, float* __restrict__ state, long long state_stride,
                                                                   const int* __restrict__ seq_starts, const int* __restrict__ state_slots, float* __restrict__ out,
-                                                                  int heads, int kv_heads, int dim, int vdim) {
+                                                                  int heads, int kv_heads, int dim, int vdim, float correct) {
   extern __shared__ __align__(16) float stage_s[];   // kDeltaStages buffers of [q: 8 R | k: 8 R | g: 8 R | v: 16 | beta | 3 unused]
   constexpr int kPadded = kDeltaLanes * R;
   constexpr int kRow = 3 * kPadded + kDeltaColumns + 4;
@@ -214,7 +221,7 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* 
         both += __shfl_xor_sync(0xffffffffu, both, offset);
       }
       const float v = cur[3 * kPadded + (tid / kDeltaLanes)], beta = cur[3 * kPadded + kDeltaColumns];
-      const float u = beta * (v - reach);
+      const float u = beta * (v - correct * reach);   // correct: 1 for the delta rule, 0 for the plain write u = beta v
 #pragma unroll
       for (int i = 0; i < R; ++i) S[i] += kk[i] * u;
       if (live && lane == 0) out[(size_t)(first + row) * heads * vdim + head * vdim + column] = read + both * u;
@@ -230,8 +237,8 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* 
 
 // a warp per (token, head)
 template <typename T>
-__global__ void delta_gate_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, const float* __restrict__ weight, T* __restrict__ out, float eps,
-                                       int vdim, size_t pairs) {
+__global__ void delta_gate_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, long long gate_stride, const float* __restrict__ weight, T* __restrict__ out,
+                                       float eps, int heads, int vdim, size_t pairs, int gate_kind) {
   const size_t pair = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (pair >= pairs) return;
   const int lane = threadIdx.x & 31;
@@ -239,16 +246,105 @@ __global__ void delta_gate_norm_kernel(const float* __restrict__ o, const T* __r
   float squares = 0.0f;
   for (int d = lane; d < vdim; d += 32) squares += row[d] * row[d];
   const float inv = rsqrtf(warp_sum(squares) / (float)vdim + eps);
-  for (int d = lane; d < vdim; d += 32) out[pair * vdim + d] = from_float<T>(row[d] * inv * weight[d] * sigmoid_f(to_float(gate[pair * vdim + d])));
+  for (int d = lane; d < vdim; d += 32) {
+    float factor = 1.0f;   // gate_kind 0: sigmoid(gate); 1: silu(gate); 2: no gate
+    if (gate_kind != 2) {
+      const float z = to_float(gate[(pair / heads) * gate_stride + (pair % heads) * vdim + d]);   // the gate may be a run of columns of wider rows
+      factor = gate_kind == 1 ? z * sigmoid_f(z) : sigmoid_f(z);
+    }
+    out[pair * vdim + d] = from_float<T>(row[d] * inv * weight[d] * factor);
+  }
+}
+
+// prep rows of the same layout for a recurrence whose forget gate also writes: rows = [q: H dim | f: H dim | v: H vdim] (products),
+// q = silu(q); f = lower + (1 - lower) sigmoid(f + f_bias) is the decay, 1 - f the key; beta = 1.  One CTA per token.
+template <typename T>
+__global__ void __launch_bounds__(256) hgrn2_prepare_kernel(const T* __restrict__ rows, int row_stride, const float* __restrict__ f_bias, const float* __restrict__ lower,
+                                                            float* __restrict__ prep, int heads, int dim, int vdim) {
+  const int t = blockIdx.x;
+  const T* row = rows + (size_t)t * row_stride;
+  const int qk = heads * dim, values = heads * vdim;
+  float* out = prep + (size_t)t * (3 * qk + values + heads);
+  for (int i = threadIdx.x; i < qk; i += blockDim.x) {
+    const float q = to_float(row[i]);
+    const float low = lower[i];
+    const float f = low + (1.0f - low) * sigmoid_f(to_float(row[qk + i]) + (f_bias != nullptr ? f_bias[i] : 0.0f));
+    out[i] = q * sigmoid_f(q);
+    out[qk + i] = 1.0f - f;
+    out[2 * qk + values + heads + i] = f;
+  }
+  for (int i = threadIdx.x; i < values; i += blockDim.x) out[2 * qk + i] = to_float(row[2 * qk + i]);
+  for (int i = threadIdx.x; i < heads; i += blockDim.x) out[2 * qk + values + i] = 1.0f;
+}
+
+// prep rows of the same layout for a state-space layer: rows = [z: inner | x: inner | B: G N | C: G N | dt: H] (products, inner = H vdim).
+// x, B and C pass a causal convolution over time per channel (taps [channels, n] with a bias, the last column the current token's;
+// inputs before an entry's first row come from the request's state at ``conv_offset``) and silu; dt = softplus(dt + dt_bias); the
+// query is C, the key B, the value x, beta = dt and the decay exp(-exp(A_log_h) dt) for all N channels of head h.  One CTA per token.
+template <typename T>
+__global__ void __launch_bounds__(256) ssd_prepare_kernel(const T* __restrict__ rows, int row_stride, const float* __restrict__ taps_w, const float* __restrict__ conv_bias,
+                                                          const float* __restrict__ a_log, const float* __restrict__ dt_bias, const float* __restrict__ state,
+                                                          long long state_stride, long long conv_offset, const int* __restrict__ token_seq,
+                                                          const int* __restrict__ seq_starts, const int* __restrict__ state_slots, float* __restrict__ prep, int heads,
+                                                          int groups, int n, int vdim, int taps) {
+  const int t = blockIdx.x;
+  const int entry = token_seq[t];
+  const int first = seq_starts[entry];
+  const int r = t - first;
+  const int inner = heads * vdim, gn = groups * n;
+  const int channels = inner + 2 * gn;
+  const float* conv_state = state + (size_t)state_slots[entry] * state_stride + conv_offset;
+  float* out = prep + (size_t)t * (2 * gn + inner + heads + heads * n);
+  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+    float sum = conv_bias != nullptr ? conv_bias[c] : 0.0f;
+    for (int j = 0; j < taps; ++j) {
+      const int back = r - (taps - 1) + j;
+      const float x = back >= 0 ? to_float(rows[(size_t)(first + back) * row_stride + inner + c]) : conv_state[(size_t)(taps - 1 + back) * channels + c];
+      sum += taps_w[c * taps + j] * x;
+    }
+    const float y = sum * sigmoid_f(sum);
+    // x -> the values; B -> the keys; C -> the queries
+    const int at = c < inner ? 2 * gn + c : (c < inner + gn ? gn + (c - inner) : c - inner - gn);
+    out[at] = y;
+  }
+  for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+    const float dt = softplus_f(to_float(rows[(size_t)t * row_stride + 2 * inner + 2 * gn + h]) + dt_bias[h]);
+    out[2 * gn + inner + h] = dt;
+    const float decay = expf(-expf(a_log[h]) * dt);
+    for (int i = 0; i < n; ++i) out[2 * gn + inner + heads + h * n + i] = decay;
+  }
+}
+
+// y = (o + D_h x) silu(z), then an RMS norm over each of ``norm_groups`` equal parts of the inner width, times a weight: the state-space
+// layer's read-out made ready for the output product.  x is read from the prep rows (their value columns).  One CTA per token.
+template <typename T>
+__global__ void __launch_bounds__(256) ssd_finish_kernel(const float* __restrict__ o, const float* __restrict__ prep, int prep_stride, int x_offset, const T* __restrict__ rows,
+                                                         int row_stride, const float* __restrict__ skip, const float* __restrict__ weight, T* __restrict__ out, float eps,
+                                                         int heads, int vdim, int norm_groups) {
+  extern __shared__ float gated_s[];
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  const int inner = heads * vdim, part = inner / norm_groups;
+  for (int i = threadIdx.x; i < inner; i += blockDim.x) {
+    const float z = to_float(rows[(size_t)t * row_stride + i]);
+    gated_s[i] = (o[(size_t)t * inner + i] + skip[i / vdim] * prep[(size_t)t * prep_stride + x_offset + i]) * (z * sigmoid_f(z));
+  }
+  __syncthreads();
+  for (int g = 0; g < norm_groups; ++g) {
+    float squares = 0.0f;
+    for (int i = threadIdx.x; i < part; i += blockDim.x) squares += gated_s[g * part + i] * gated_s[g * part + i];
+    const float inv = 1.0f / sqrtf(block_sum(squares, scratch) / (float)part + eps);
+    for (int i = threadIdx.x; i < part; i += blockDim.x) out[(size_t)t * inner + g * part + i] = from_float<T>(gated_s[g * part + i] * inv * weight[g * part + i]);
+  }
 }
 
 template <int R>
 static int launch_delta_rule(const float* prep, float* state, long long state_stride, const int* seq_starts, const int* state_slots, float* out, int entries,
-                             int heads, int kv_heads, int dim, int vdim, cudaStream_t stream) {
+                             int heads, int kv_heads, int dim, int vdim, float correct, cudaStream_t stream) {
   const int column_blocks = (vdim + kDeltaColumns - 1) / kDeltaColumns;
   const size_t smem = kDeltaStages * (size_t)(3 * kDeltaLanes * R + kDeltaColumns + 4) * sizeof(float);
   delta_rule_kernel<R><<<dim3(heads * column_blocks, entries), kDeltaThreads, smem, stream>>>(prep, state, state_stride, seq_starts, state_slots, out, heads, kv_heads,
-                                                                                           dim, vdim);
+                                                                                           dim, vdim, correct);
   return (int)cudaGetLastError();
 }
 
@@ -256,7 +352,8 @@ static int launch_delta_rule(const float* prep, float* state, long long state_st
 
 using namespace tlie;
 
-TLIE_EXPORT int tlie_delta_prepare(int dtype, const void* rows, int row_stride, int beta_offset, const void* a, const float* taps_w, const float* a_log,
+TLIE_EXPORT int tlie_delta_prepare(int dtype, const void* rows, int row_stride, int beta_offset, const void* a, long long a_stride, int decay_per_head,
+                                   const float* taps_w, const float* a_log,
                                    const float* dt_bias, float* state, long long state_stride, long long conv_offset, const int* token_seq, const int* seq_starts,
                                    const int* state_slots, float* prep, int tokens, int entries, int heads, int kv_heads, int dim, int vdim, int taps, float unit_eps,
                                    float q_scale, cudaStream_t stream) {
@@ -266,10 +363,10 @@ TLIE_EXPORT int tlie_delta_prepare(int dtype, const void* rows, int row_stride, 
   if (dim > 256) return (int)cudaErrorInvalidValue;
   const dim3 parts(tokens, 2 * kv_heads + heads);
   if (dtype == TLIE_F32)
-    delta_prepare_kernel<float><<<parts, 128, 0, stream>>>((const float*)rows, row_stride, beta_offset, (const float*)a, taps_w, a_log, dt_bias, state, state_stride,
+    delta_prepare_kernel<float><<<parts, 128, 0, stream>>>((const float*)rows, row_stride, beta_offset, (const float*)a, a_stride, decay_per_head, taps_w, a_log, dt_bias, state, state_stride,
                                                            conv_offset, token_seq, seq_starts, state_slots, prep, heads, kv_heads, dim, vdim, taps, unit_eps, q_scale);
   else
-    delta_prepare_kernel<__nv_bfloat16><<<parts, 128, 0, stream>>>((const __nv_bfloat16*)rows, row_stride, beta_offset, (const __nv_bfloat16*)a, taps_w, a_log, dt_bias,
+    delta_prepare_kernel<__nv_bfloat16><<<parts, 128, 0, stream>>>((const __nv_bfloat16*)rows, row_stride, beta_offset, (const __nv_bfloat16*)a, a_stride, decay_per_head, taps_w, a_log, dt_bias,
                                                                    state, state_stride, conv_offset, token_seq, seq_starts, state_slots, prep, heads, kv_heads, dim,
                                                                    vdim, taps, unit_eps, q_scale);
   cudaError_t status = cudaGetLastError();
@@ -284,12 +381,12 @@ TLIE_EXPORT int tlie_delta_prepare(int dtype, const void* rows, int row_stride, 
 }
 
 TLIE_EXPORT int tlie_delta_rule(const float* prep, float* state, long long state_stride, const int* seq_starts, const int* state_slots, float* out, int entries,
-                                int heads, int kv_heads, int dim, int vdim, cudaStream_t stream) {
+                                int heads, int kv_heads, int dim, int vdim, int plain, cudaStream_t stream) {
   if (entries <= 0) return 0;
   if (dim < 1 || dim > 256 || kv_heads < 1 || heads % kv_heads != 0) return (int)cudaErrorInvalidValue;
   const int r = 4 * ((dim + 4 * kDeltaLanes - 1) / (4 * kDeltaLanes));
 #define TLIE_DELTA(R) \
-  if (r <= R) return launch_delta_rule<R>(prep, state, state_stride, seq_starts, state_slots, out, entries, heads, kv_heads, dim, vdim, stream)
+  if (r <= R) return launch_delta_rule<R>(prep, state, state_stride, seq_starts, state_slots, out, entries, heads, kv_heads, dim, vdim, plain ? 0.0f : 1.0f, stream)
   TLIE_DELTA(4);
   TLIE_DELTA(8);
   TLIE_DELTA(12);
@@ -300,14 +397,64 @@ TLIE_EXPORT int tlie_delta_rule(const float* prep, float* state, long long state
   return (int)cudaErrorInvalidValue;
 }
 
-TLIE_EXPORT int tlie_delta_gate_norm(int dtype, const float* o, const void* gate, const float* weight, void* out, float eps, int tokens, int heads, int vdim,
-                                     cudaStream_t stream) {
+TLIE_EXPORT int tlie_delta_gate_norm(int dtype, const float* o, const void* gate, long long gate_stride, const float* weight, void* out, float eps, int tokens, int heads,
+                                     int vdim, int gate_kind, cudaStream_t stream) {
   const size_t pairs = (size_t)tokens * heads;
   if (pairs == 0) return 0;
+  if (gate_kind < 0 || gate_kind > 2 || (gate_kind != 2 && gate == nullptr)) return (int)cudaErrorInvalidValue;
   const int blocks = (int)((pairs + 3) / 4);
   if (dtype == TLIE_F32)
-    delta_gate_norm_kernel<float><<<blocks, 128, 0, stream>>>(o, (const float*)gate, weight, (float*)out, eps, vdim, pairs);
+    delta_gate_norm_kernel<float><<<blocks, 128, 0, stream>>>(o, (const float*)gate, gate_stride, weight, (float*)out, eps, heads, vdim, pairs, gate_kind);
   else
-    delta_gate_norm_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(o, (const __nv_bfloat16*)gate, weight, (__nv_bfloat16*)out, eps, vdim, pairs);
+    delta_gate_norm_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>(o, (const __nv_bfloat16*)gate, gate_stride, weight, (__nv_bfloat16*)out, eps, heads, vdim, pairs, gate_kind);
+  return (int)cudaGetLastError();
+}
+
+TLIE_EXPORT int tlie_hgrn2_prepare(int dtype, const void* rows, int row_stride, const float* f_bias, const float* lower, float* prep, int tokens, int heads, int dim,
+                                   int vdim, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (dtype == TLIE_F32)
+    hgrn2_prepare_kernel<float><<<tokens, 256, 0, stream>>>((const float*)rows, row_stride, f_bias, lower, prep, heads, dim, vdim);
+  else
+    hgrn2_prepare_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)rows, row_stride, f_bias, lower, prep, heads, dim, vdim);
+  return (int)cudaGetLastError();
+}
+
+// The convolution's inputs (columns [inner, inner + channels) of ``rows``) are moved on in the request's state afterwards.
+TLIE_EXPORT int tlie_ssd_prepare(int dtype, const void* rows, int row_stride, const float* taps_w, const float* conv_bias, const float* a_log, const float* dt_bias,
+                                 float* state, long long state_stride, long long conv_offset, const int* token_seq, const int* seq_starts, const int* state_slots,
+                                 float* prep, int tokens, int entries, int heads, int groups, int n, int vdim, int taps, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (taps < 1 || taps > kDeltaMaxTaps || groups < 1 || heads % groups != 0) return (int)cudaErrorInvalidValue;
+  const int inner = heads * vdim, channels = inner + 2 * groups * n;
+  if (dtype == TLIE_F32)
+    ssd_prepare_kernel<float><<<tokens, 256, 0, stream>>>((const float*)rows, row_stride, taps_w, conv_bias, a_log, dt_bias, state, state_stride, conv_offset, token_seq,
+                                                          seq_starts, state_slots, prep, heads, groups, n, vdim, taps);
+  else
+    ssd_prepare_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)rows, row_stride, taps_w, conv_bias, a_log, dt_bias, state, state_stride,
+                                                                  conv_offset, token_seq, seq_starts, state_slots, prep, heads, groups, n, vdim, taps);
+  cudaError_t status = cudaGetLastError();
+  if (status != cudaSuccess || taps == 1) return (int)status;
+  const dim3 grid((channels + 127) / 128, entries);
+  if (dtype == TLIE_F32)
+    delta_conv_state_kernel<float><<<grid, 128, 0, stream>>>((const float*)rows + inner, row_stride, state, state_stride, conv_offset, seq_starts, state_slots, channels, taps);
+  else
+    delta_conv_state_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)rows + inner, row_stride, state, state_stride, conv_offset, seq_starts,
+                                                                     state_slots, channels, taps);
+  return (int)cudaGetLastError();
+}
+
+TLIE_EXPORT int tlie_ssd_finish(int dtype, const float* o, const float* prep, int prep_stride, int x_offset, const void* rows, int row_stride, const float* skip,
+                                const float* weight, void* out, float eps, int tokens, int heads, int vdim, int norm_groups, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  const int inner = heads * vdim;
+  if (norm_groups < 1 || inner % norm_groups != 0 || (size_t)inner * sizeof(float) > 48 * 1024) return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)inner * sizeof(float);
+  if (dtype == TLIE_F32)
+    ssd_finish_kernel<float><<<tokens, 256, smem, stream>>>(o, prep, prep_stride, x_offset, (const float*)rows, row_stride, skip, weight, (float*)out, eps, heads, vdim,
+                                                            norm_groups);
+  else
+    ssd_finish_kernel<__nv_bfloat16><<<tokens, 256, smem, stream>>>(o, prep, prep_stride, x_offset, (const __nv_bfloat16*)rows, row_stride, skip, weight,
+                                                                    (__nv_bfloat16*)out, eps, heads, vdim, norm_groups);
   return (int)cudaGetLastError();
 }

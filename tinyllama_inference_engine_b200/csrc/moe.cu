@@ -220,7 +220,7 @@ constexpr int kRouteWarps = 4;
 
 // One warp chooses a token's experts from s [experts] and choice [experts] (shared memory, written before); group_score [groups] is scratch.
 __device__ __forceinline__ void route_select(float* s, float* choice, float* group_score, int* __restrict__ ids, float* __restrict__ weights, int t, int lane,
-                                             int experts, int groups, int keep, int top, float route_scale) {
+                                             int experts, int groups, int keep, int top, float route_scale, int normalize) {
   const int per = experts / groups;
   if (groups > 1 && keep < groups) {
     for (int g = lane; g < groups; g += 32) {
@@ -277,7 +277,7 @@ __device__ __forceinline__ void route_select(float* s, float* choice, float* gro
     total += s[e];
     __syncwarp();
   }
-  const float factor = route_scale / (total + 1e-20f);
+  const float factor = normalize ? route_scale / (total + 1e-20f) : route_scale;   // not normalised: the scores as they are
   for (int k = lane; k < top; k += 32) weights[(size_t)t * top + k] *= factor;
 }
 
@@ -285,7 +285,7 @@ __device__ __forceinline__ void route_select(float* s, float* choice, float* gro
 template <typename T>
 __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router, const float* __restrict__ correction,
                                                                      int* __restrict__ ids, float* __restrict__ weights, int tokens, int width, int experts,
-                                                                     int groups, int keep, int top, float route_scale) {
+                                                                     int groups, int keep, int top, float route_scale, int normalize) {
   extern __shared__ float route_smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * kRouteWarps + warp;
@@ -306,7 +306,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(const T* __
     }
   }
   __syncwarp();
-  route_select(s, choice, group_score, ids, weights, t, lane, experts, groups, keep, top, route_scale);
+  route_select(s, choice, group_score, ids, weights, t, lane, experts, groups, keep, top, route_scale, normalize);
 }
 
 constexpr int kRouteTiledWarps = 8;    // steps of many tokens (four share a CTA); a CTA of one token has 16 warps
@@ -320,7 +320,7 @@ template <typename T, int TOK, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32) moe_route_tiled_kernel(const T* __restrict__ x, const float* __restrict__ router,
                                                                                 const float* __restrict__ correction, int* __restrict__ ids,
                                                                                 float* __restrict__ weights, int tokens, int width, int experts, int groups, int keep,
-                                                                                int top, float route_scale) {
+                                                                                int top, float route_scale, int normalize) {
   extern __shared__ __align__(16) float route_smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t0 = blockIdx.x * TOK;
@@ -380,7 +380,7 @@ __global__ void __launch_bounds__(WARPS * 32) moe_route_tiled_kernel(const T* __
   for (int i = warp; i < TOK; i += WARPS) {
     if (t0 + i >= tokens) break;
     float* s = tables + (size_t)i * per_token;
-    route_select(s, s + experts, s + 2 * experts, ids, weights, t0 + i, lane, experts, groups, keep, top, route_scale);
+    route_select(s, s + experts, s + 2 * experts, ids, weights, t0 + i, lane, experts, groups, keep, top, route_scale, normalize);
   }
 }
 
@@ -391,11 +391,12 @@ constexpr int kDownOutputs = 32;
 // grid (tokens * top, ceil(ff / 32)); act [tokens * top][ff]
 template <typename T>
 __global__ void __launch_bounds__(kMoeWarps * 32) moe_gate_up_kernel(const T* __restrict__ x, const T* __restrict__ gate_up, const int* __restrict__ ids,
-                                                                     T* __restrict__ act, int width, int ff, int top, int kind) {
+                                                                     const float* __restrict__ input_weights, T* __restrict__ act, int width, int ff, int top, int kind) {
   extern __shared__ float moe_x[];
   const int slot = blockIdx.x, t = slot / top;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int d = threadIdx.x; d < width; d += blockDim.x) moe_x[d] = to_float(x[(size_t)t * width + d]);
+  const float scale = input_weights != nullptr ? input_weights[slot] : 1.0f;   // an expert that reads its token times the token's weight
+  for (int d = threadIdx.x; d < width; d += blockDim.x) moe_x[d] = to_float(x[(size_t)t * width + d]) * scale;
   __syncthreads();
   const T* expert = gate_up + (size_t)ids[slot] * 2 * ff * width;
   const bool vector = rows_are_vectors(expert, width);
@@ -460,7 +461,7 @@ __global__ void __launch_bounds__(kMoeWarps * 32, 4) moe_down_kernel(const T* __
 #pragma unroll
         for (int o = 0; o < 2; ++o) {
           const float dot = warp_sum(sums[o][j]);
-          if (k0 + j < top) total[o] += weights[(size_t)t * top + k0 + j] * dot;
+          if (k0 + j < top) total[o] += (weights != nullptr ? weights[(size_t)t * top + k0 + j] : 1.0f) * dot;
         }
       }
     }
@@ -479,7 +480,7 @@ __global__ void __launch_bounds__(kMoeWarps * 32, 4) moe_down_kernel(const T* __
 using namespace tlie;
 
 TLIE_EXPORT int tlie_moe_route(int dtype, const void* x, const float* router, const float* correction, int* ids, float* weights, int tokens, int width, int experts,
-                               int groups, int keep, int top, float route_scale, cudaStream_t stream) {
+                               int groups, int keep, int top, float route_scale, int normalize, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (experts <= 0 || groups <= 0 || experts % groups != 0 || keep <= 0 || keep > groups || top <= 0 || top > keep * (experts / groups))
     return (int)cudaErrorInvalidValue;
@@ -496,7 +497,7 @@ TLIE_EXPORT int tlie_moe_route(int dtype, const void* x, const float* router, co
     if (tiled > 48 * 1024) e = cudaFuncSetAttribute(moe_route_tiled_kernel<T, TOK, (TOK == 1 ? 16 : kRouteTiledWarps)>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tiled);             \
     if (e == cudaSuccess)                                                                                                                                 \
       moe_route_tiled_kernel<T, TOK, (TOK == 1 ? 16 : kRouteTiledWarps)><<<blocks, (TOK == 1 ? 16 : kRouteTiledWarps) * 32, tiled, stream>>>((const T*)x, router, correction, ids, weights, tokens, width, experts, groups, keep, \
-                                                                                     top, route_scale);                                                  \
+                                                                                     top, route_scale, normalize);                                                  \
   } while (0)
       if (dtype == TLIE_F32) {
         if (tok == 4) TLIE_ROUTE_TILED(float, 4); else TLIE_ROUTE_TILED(float, 1);
@@ -511,16 +512,16 @@ TLIE_EXPORT int tlie_moe_route(int dtype, const void* x, const float* router, co
   if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
   const int blocks = (tokens + kRouteWarps - 1) / kRouteWarps;
   if (dtype == TLIE_F32)
-    moe_route_kernel<float><<<blocks, kRouteWarps * 32, smem, stream>>>((const float*)x, router, correction, ids, weights, tokens, width, experts, groups, keep, top, route_scale);
+    moe_route_kernel<float><<<blocks, kRouteWarps * 32, smem, stream>>>((const float*)x, router, correction, ids, weights, tokens, width, experts, groups, keep, top, route_scale, normalize);
   else
     moe_route_kernel<__nv_bfloat16><<<blocks, kRouteWarps * 32, smem, stream>>>((const __nv_bfloat16*)x, router, correction, ids, weights, tokens, width, experts, groups,
-                                                                              keep, top, route_scale);
+                                                                              keep, top, route_scale, normalize);
   return (int)cudaGetLastError();
 }
 
 template <typename T>
 static int launch_moe_experts(const void* x, const void* gate_up, const void* down, const int* ids, const float* weights, const void* shared, void* act, void* out,
-                              int tokens, int width, int ff, int top, int kind, cudaStream_t stream) {
+                              int tokens, int width, int ff, int top, int kind, int weight_input, cudaStream_t stream) {
   const size_t x_smem = (size_t)width * sizeof(float), act_smem = (size_t)top * ff * sizeof(float);
   if (x_smem > 200 * 1024 || act_smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   cudaError_t e;
@@ -533,19 +534,20 @@ static int launch_moe_experts(const void* x, const void* gate_up, const void* do
     if (e != cudaSuccess) return (int)e;
   }
   moe_gate_up_kernel<T><<<dim3(tokens * top, (ff + kGateUpOutputs - 1) / kGateUpOutputs), kMoeWarps * 32, x_smem, stream>>>(
-      (const T*)x, (const T*)gate_up, ids, (T*)act, width, ff, top, kind);
+      (const T*)x, (const T*)gate_up, ids, weight_input ? weights : nullptr, (T*)act, width, ff, top, kind);
   e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   moe_down_kernel<T><<<dim3(tokens, (width + kDownOutputs - 1) / kDownOutputs), kMoeWarps * 32, act_smem, stream>>>(
-      (const T*)act, (const T*)down, ids, weights, (const T*)shared, (T*)out, width, ff, top);
+      (const T*)act, (const T*)down, ids, weight_input ? nullptr : weights, (const T*)shared, (T*)out, width, ff, top);
   return (int)cudaGetLastError();
 }
 
-// ``act``: scratch [tokens * top, ff] of ``dtype``; ``shared`` [tokens, width] or null; ``out`` [tokens, width].
+// ``act``: scratch [tokens * top, ff] of ``dtype``; ``shared`` [tokens, width] or null; ``out`` [tokens, width].  ``weight_input`` 1: a chosen expert reads
+// the token times its weight and its output is added as it is (out[t] = sum_k expert_k(weight_k x[t])); 0: the weight multiplies the expert's output.
 TLIE_EXPORT int tlie_moe_experts(int dtype, const void* x, const void* gate_up, const void* down, const int* ids, const float* weights, const void* shared, void* act,
-                                 void* out, int tokens, int width, int ff, int top, int kind, cudaStream_t stream) {
+                                 void* out, int tokens, int width, int ff, int top, int kind, int weight_input, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if ((long long)tokens * top > 2147483647LL / 2 || kind < 0 || kind > 1) return (int)cudaErrorInvalidValue;
-  if (dtype == TLIE_F32) return launch_moe_experts<float>(x, gate_up, down, ids, weights, shared, act, out, tokens, width, ff, top, kind, stream);
-  return launch_moe_experts<__nv_bfloat16>(x, gate_up, down, ids, weights, shared, act, out, tokens, width, ff, top, kind, stream);
+  if (dtype == TLIE_F32) return launch_moe_experts<float>(x, gate_up, down, ids, weights, shared, act, out, tokens, width, ff, top, kind, weight_input, stream);
+  return launch_moe_experts<__nv_bfloat16>(x, gate_up, down, ids, weights, shared, act, out, tokens, width, ff, top, kind, weight_input, stream);
 }

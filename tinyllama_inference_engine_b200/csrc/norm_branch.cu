@@ -32,6 +32,19 @@ __device__ __forceinline__ void row_statistics(const float* row, int width, int 
   inv = 1.0f / sqrtf(block_sum(squares, scratch) / (float)width + eps);
 }
 
+// The same per group: a row cut into ``groups`` equal consecutive parts, each with statistics of its own, left in shared memory
+// (``means`` and ``invs``, one entry per group) for all threads.  One group is the whole row, summed in the order it always was.
+constexpr int kNormMaxGroups = 64;
+__device__ __forceinline__ void group_statistics(const float* row, int width, int groups, int centred, float eps, float* scratch, float* means, float* invs) {
+  const int part = width / groups;
+  for (int g = 0; g < groups; ++g) {
+    float mean, inv;
+    row_statistics(row + g * part, part, centred, eps, scratch, mean, inv);
+    if (threadIdx.x == 0) means[g] = mean, invs[g] = inv;
+  }
+  __syncthreads();
+}
+
 // eight neighbours of a row at once, 16 bytes a load: a row of a few thousand numbers is then one or two loads per thread, all of them
 // in flight together, where a number per load made every pass of a step of few rows wait for memory several times over
 __device__ __forceinline__ void load8(const float* src, float (&v)[8]) {
@@ -64,12 +77,13 @@ __device__ __forceinline__ void store8(__nv_bfloat16* dst, const float (&v)[8]) 
 template <typename TY, typename TO>
 __global__ void __launch_bounds__(kNormThreads) branch_norm_wide_kernel(float* __restrict__ residual, const TY* __restrict__ y, const float* __restrict__ post_weight,
                                                                         const float* __restrict__ next_weight, TO* __restrict__ out, const int* __restrict__ rows,
-                                                                        float eps, int centred, int width) {
+                                                                        float eps, int centred, int width, int groups) {
   extern __shared__ __align__(16) float norm_row[];
   __shared__ float scratch[32];
+  __shared__ float means[kNormMaxGroups], invs[kNormMaxGroups];
   const int source = rows != nullptr ? rows[blockIdx.x] : blockIdx.x;
   float* stream = residual + (size_t)source * width;
-  float mean, inv;
+  const int part = width / groups;   // a multiple of 8 here: a run of eight lies in one group
   float a[8], b[8], w[8];
   if (y != nullptr) {
     const TY* branch = y + (size_t)source * width;
@@ -78,11 +92,12 @@ __global__ void __launch_bounds__(kNormThreads) branch_norm_wide_kernel(float* _
       store8(norm_row + i, a);
     }
     __syncthreads();
-    row_statistics(norm_row, width, centred, eps, scratch, mean, inv);
+    group_statistics(norm_row, width, groups, centred, eps, scratch, means, invs);
     for (int i = threadIdx.x * 8; i < width; i += blockDim.x * 8) {   // a thread's own runs again
       load8(stream + i, b);
       load8(post_weight + i, w);
       load8(norm_row + i, a);
+      const float mean = means[i / part], inv = invs[i / part];
 #pragma unroll
       for (int j = 0; j < 8; ++j) b[j] = b[j] + ((a[j] - mean) * inv) * w[j];
       store8(stream + i, b);
@@ -96,11 +111,12 @@ __global__ void __launch_bounds__(kNormThreads) branch_norm_wide_kernel(float* _
   }
   if (out == nullptr) return;
   __syncthreads();
-  row_statistics(norm_row, width, centred, eps, scratch, mean, inv);
+  group_statistics(norm_row, width, groups, centred, eps, scratch, means, invs);
   TO* dst = out + (size_t)blockIdx.x * width;
   for (int i = threadIdx.x * 8; i < width; i += blockDim.x * 8) {
     load8(next_weight + i, w);
     load8(norm_row + i, a);
+    const float mean = means[i / part], inv = invs[i / part];
 #pragma unroll
     for (int j = 0; j < 8; ++j) a[j] = ((a[j] - mean) * inv) * w[j];
     store8(dst + i, a);
@@ -110,19 +126,20 @@ __global__ void __launch_bounds__(kNormThreads) branch_norm_wide_kernel(float* _
 template <typename TY, typename TO>
 __global__ void __launch_bounds__(kNormThreads) branch_norm_kernel(float* __restrict__ residual, const TY* __restrict__ y, const float* __restrict__ post_weight,
                                                                    const float* __restrict__ next_weight, TO* __restrict__ out, const int* __restrict__ rows,
-                                                                   float eps, int centred, int width) {
+                                                                   float eps, int centred, int width, int groups) {
   extern __shared__ float norm_row[];
   __shared__ float scratch[32];
+  __shared__ float means[kNormMaxGroups], invs[kNormMaxGroups];
   const int source = rows != nullptr ? rows[blockIdx.x] : blockIdx.x;
   float* stream = residual + (size_t)source * width;
-  float mean, inv;
+  const int part = width / groups;
   if (y != nullptr) {
     const TY* branch = y + (size_t)source * width;
     for (int i = threadIdx.x; i < width; i += blockDim.x) norm_row[i] = to_float(branch[i]);
     __syncthreads();
-    row_statistics(norm_row, width, centred, eps, scratch, mean, inv);
+    group_statistics(norm_row, width, groups, centred, eps, scratch, means, invs);
     for (int i = threadIdx.x; i < width; i += blockDim.x) {   // every thread rereads what it wrote itself
-      const float v = stream[i] + ((norm_row[i] - mean) * inv) * post_weight[i];
+      const float v = stream[i] + ((norm_row[i] - means[i / part]) * invs[i / part]) * post_weight[i];
       stream[i] = v;
       norm_row[i] = v;
     }
@@ -131,9 +148,9 @@ __global__ void __launch_bounds__(kNormThreads) branch_norm_kernel(float* __rest
   }
   if (out == nullptr) return;
   __syncthreads();
-  row_statistics(norm_row, width, centred, eps, scratch, mean, inv);
+  group_statistics(norm_row, width, groups, centred, eps, scratch, means, invs);
   TO* dst = out + (size_t)blockIdx.x * width;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_float<TO>(((norm_row[i] - mean) * inv) * next_weight[i]);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_float<TO>(((norm_row[i] - means[i / part]) * invs[i / part]) * next_weight[i]);
 }
 
 template <typename T>
@@ -156,7 +173,7 @@ __global__ void stream_with_embedding_kernel(const float* __restrict__ residual,
 
 template <typename TY, typename TO>
 static int launch_branch_norm(float* residual, const void* y, const float* post_weight, const float* next_weight, void* out, const int* rows, float eps,
-                              int centred, int count, int width, cudaStream_t stream) {
+                              int centred, int count, int width, int groups, cudaStream_t stream) {
   const size_t smem = (size_t)width * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   if (smem > 48 * 1024) {
@@ -164,15 +181,15 @@ static int launch_branch_norm(float* residual, const void* y, const float* post_
     if (e != cudaSuccess) return (int)e;
   }
   const auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
-  if (width % 8 == 0 && aligned(residual) && aligned(y) && aligned(post_weight) && aligned(next_weight) && aligned(out)) {
+  if (width % 8 == 0 && (width / groups) % 8 == 0 && aligned(residual) && aligned(y) && aligned(post_weight) && aligned(next_weight) && aligned(out)) {
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(branch_norm_wide_kernel<TY, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
     }
-    branch_norm_wide_kernel<TY, TO><<<count, kNormThreads, smem, stream>>>(residual, (const TY*)y, post_weight, next_weight, (TO*)out, rows, eps, centred, width);
+    branch_norm_wide_kernel<TY, TO><<<count, kNormThreads, smem, stream>>>(residual, (const TY*)y, post_weight, next_weight, (TO*)out, rows, eps, centred, width, groups);
     return (int)cudaGetLastError();
   }
-  branch_norm_kernel<TY, TO><<<count, kNormThreads, smem, stream>>>(residual, (const TY*)y, post_weight, next_weight, (TO*)out, rows, eps, centred, width);
+  branch_norm_kernel<TY, TO><<<count, kNormThreads, smem, stream>>>(residual, (const TY*)y, post_weight, next_weight, (TO*)out, rows, eps, centred, width, groups);
   return (int)cudaGetLastError();
 }
 
@@ -182,13 +199,14 @@ using namespace tlie;
 
 // ``count`` rows are worked on: all of the stream's, or with ``rows`` the listed ones (then y must be null: a gathered norm adds nothing).
 // ``y`` and ``out`` are of ``dtype``; either may be null.
+// ``groups``: the norms' statistics are taken over each of that many equal consecutive parts of a row (1: over the whole row).
 TLIE_EXPORT int tlie_branch_norm(int dtype, float* residual, const void* y, const float* post_weight, const float* next_weight, void* out, const int* rows,
-                                 float eps, int centred, int count, int width, cudaStream_t stream) {
+                                 float eps, int centred, int count, int width, int groups, cudaStream_t stream) {
   if (count <= 0) return 0;
-  if (width <= 0 || (rows != nullptr && y != nullptr) || (y != nullptr && post_weight == nullptr) || (out != nullptr && next_weight == nullptr))
+  if (groups < 1 || groups > kNormMaxGroups || width % groups != 0 || width <= 0 || (rows != nullptr && y != nullptr) || (y != nullptr && post_weight == nullptr) || (out != nullptr && next_weight == nullptr))
     return (int)cudaErrorInvalidValue;
-  if (dtype == TLIE_F32) return launch_branch_norm<float, float>(residual, y, post_weight, next_weight, out, rows, eps, centred, count, width, stream);
-  return launch_branch_norm<__nv_bfloat16, __nv_bfloat16>(residual, y, post_weight, next_weight, out, rows, eps, centred, count, width, stream);
+  if (dtype == TLIE_F32) return launch_branch_norm<float, float>(residual, y, post_weight, next_weight, out, rows, eps, centred, count, width, groups, stream);
+  return launch_branch_norm<__nv_bfloat16, __nv_bfloat16>(residual, y, post_weight, next_weight, out, rows, eps, centred, count, width, groups, stream);
 }
 
 TLIE_EXPORT int tlie_stream_with_embedding(int dtype, const float* residual, const void* table, const int* ids, float scale, void* out, int rows, int width,

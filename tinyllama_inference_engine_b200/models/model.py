@@ -15,9 +15,15 @@ def expected_tensors(spec: ModelSpec) -> list[TensorSpec]:
     return specs
 
 
+EMBEDDING_STREAM = -1   # the cache stream of an embedding that keeps something per request (its ``cache_need``)
+
+
 def cache_needs(spec: ModelSpec) -> dict[int, CacheNeed]:
-    """What each cache stream of the order list needs (decided by the run that writes it)."""
+    """What each cache stream of the order list needs (decided by the run that writes it); an embedding with a need of its own has the stream ``EMBEDDING_STREAM``."""
     needs: dict[int, CacheNeed] = {}
+    embedding = part_class("embedding", spec.embedding)
+    if hasattr(embedding, "cache_need") and embedding.cache_need(spec.embedding).kind != "none":
+        needs[EMBEDDING_STREAM] = embedding.cache_need(spec.embedding)
     for entry in spec.order:
         if entry.writes_cache:
             block = spec.layers[entry.layer].block
@@ -54,7 +60,10 @@ class DecoderModel:
         """The complete residual stream of the step's rows, and a lazy final norm of it if the last block left one prepared."""
         from .. import ops
 
-        residual = self.embedding.forward(ctx.token_ids, ctx)
+        if EMBEDDING_STREAM in self.cache_needs:
+            residual = self.embedding.forward(ctx.token_ids, ctx, caches[EMBEDDING_STREAM])
+        else:
+            residual = self.embedding.forward(ctx.token_ids, ctx)
         pending = None
         order = self.spec.order
         for index, entry in enumerate(order):

@@ -24,6 +24,7 @@ MIXED_ATTENTION_SOURCES = ["attention_mixed.cu"]   # likewise for attention with
 DELTA_RULE_SOURCES = ["delta_rule.cu"]             # likewise for the gated delta rule
 DIFF_ATTENTION_SOURCES = ["attention_diff.cu"]     # likewise for differential attention
 MOE_SOURCES = ["moe.cu", "moe_grouped.cu", "moe_grouped_tc.cu"]   # likewise for a feed-forward of routed experts
+SEQUENCE_SOURCES = ["sequence_filters.cu"]         # likewise for an embedding that reads the token before, a convolution in front of a sublayer
 _F32, _BF16 = 0, 1
 launch_count = 0  # kernels of this engine launched by this process (a claim the bench reports)
 
@@ -41,7 +42,8 @@ def build_all() -> list:
     """Compile every kernel set (used by the build check); returns the library paths."""
     return [build_library("tlie_core", CORE_SOURCES), build_library("tlie_recurrent", RECURRENT_SOURCES),
             build_library("tlie_attention_mixed", MIXED_ATTENTION_SOURCES), build_library(f"tlie_delta_rule_l{DELTA_LANES}", DELTA_RULE_SOURCES, {"TLIE_DELTA_LANES": DELTA_LANES}),
-            build_library("tlie_attention_diff", DIFF_ATTENTION_SOURCES), build_library("tlie_moe", MOE_SOURCES)] + fast.build_all()
+            build_library("tlie_attention_diff", DIFF_ATTENTION_SOURCES), build_library("tlie_moe", MOE_SOURCES),
+            build_library("tlie_sequence", SEQUENCE_SOURCES)] + fast.build_all()
 
 
 def _code(tensor: torch.Tensor) -> int:
@@ -203,12 +205,15 @@ def gate_mul(gate_up, out, kind: str = "silu") -> None:
     _check(core().tlie_gate_mul(_code(out), _ptr(gate_up), _ptr(out), c_int(rows), c_int(inter), c_int(GATE_KINDS[kind]), _stream()), "gate_mul")
 
 
-def branch_norm(residual, y, post_weight, next_weight, out, eps: float, centred: bool = True, rows=None) -> None:
+def branch_norm(residual, y, post_weight, next_weight, out, eps: float, centred: bool = True, rows=None, groups: int = 1) -> None:
     """One kernel around a residual branch: ``residual += norm(y) * post_weight`` (if ``y`` is given), then
     ``out = norm(residual[rows]) * next_weight`` (if ``out`` is given; ``rows`` None: every row in order, and only then may ``y`` be given).
     ``centred``: the layer norm without a bias, (x - mean) / sqrt(mean((x - mean)^2) + eps); else x / sqrt(mean(x^2) + eps).
+    ``groups``: the statistics are taken over each of that many equal consecutive parts of a row.
     The stream, the statistics and the weights are 32-bit; ``y`` and ``out`` share a dtype."""
     width = residual.shape[1]
+    if groups < 1 or width % groups:
+        raise KernelError(f"branch_norm: a row of {width} cannot be cut into {groups} equal parts", code="invalid_shape")
     count = residual.shape[0] if rows is None else rows.shape[0]
     if residual.dtype != torch.float32 or (y is not None and (y.shape != residual.shape or rows is not None)) or (out is not None and out.shape != (count, width)):
         raise KernelError("branch_norm: a 32-bit stream [T, width], y of its shape, out [rows, width]", code="invalid_shape")
@@ -221,7 +226,7 @@ def branch_norm(residual, y, post_weight, next_weight, out, eps: float, centred:
         return
     _check(core().tlie_branch_norm(_code(y if y is not None else out), _ptr(residual), _ptr(y), _ptr(post_weight if y is not None else None),
                                    _ptr(next_weight if out is not None else None), _ptr(out), _i32(rows, "rows"), c_float(eps), c_int(1 if centred else 0),
-                                   c_int(count), c_int(width), _stream()), "branch_norm")
+                                   c_int(count), c_int(width), c_int(groups), _stream()), "branch_norm")
 
 
 def stream_with_embedding(residual, table, ids, scale: float, out) -> None:
@@ -574,48 +579,164 @@ def delta_state_words(heads: int, dim: int, vdim: int, channels: int, taps: int)
     return matrices + (taps - 1) * channels, matrices
 
 
+def _state_rows(state, what: str):
+    """(pointer, words between two requests' slots) of a per-request state [slots, words] in 32-bit; it may be a run of columns of wider rows."""
+    if state is None or state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or not state.is_cuda:
+        raise KernelError(f"{what}: the per-request state is 32-bit [slots, words] on a CUDA device", code="invalid_shape")
+    return c_void_p(state.data_ptr()), c_longlong(state.stride(0))
+
+
 def delta_prepare(rows, beta_offset: int, decay_in, taps, a_log, dt_bias, state, conv_offset: int, ctx, prep, heads: int, kv_heads: int, dim: int, vdim: int,
-                  unit_eps: float, q_scale: float) -> None:
+                  unit_eps: float, q_scale: float, decay_per_head: bool = False) -> None:
     """What the delta rule's recurrence reads, per token, in 32-bit: ``prep[t] = [q | k | v | beta | decay]``.
 
     ``rows`` [T, >= channels + heads] starts with the products for q, k (``kv_heads * dim`` each) and v (``heads * vdim``) and holds the
     beta pre-activations from ``beta_offset``.  q, k, v pass a causal convolution over time per channel (``taps`` [channels, n], last
     column the current token's; the inputs before an entry's first row are read from the request's state at ``conv_offset``) and silu;
     q and k become unit vectors per head (``unit_eps`` inside the root), q times ``q_scale``; beta = sigmoid; decay =
-    exp(-exp(a_log[h]) softplus(decay_in + dt_bias)) per head and key channel.  Afterwards the state's convolution inputs are moved on."""
+    exp(-exp(a_log[h]) softplus(decay_in + dt_bias)) per head and key channel.  Afterwards the state's convolution inputs are moved on.
+    ``decay_per_head``: ``decay_in`` [T, heads] (it may be a run of columns of ``rows``) and ``dt_bias`` [heads] give one decay per head, for all its key channels."""
     tokens = rows.shape[0]
+    decays = heads if decay_per_head else heads * dim
     channels = 2 * kv_heads * dim + heads * vdim
     width = channels + heads + heads * dim
     if prep.shape != (tokens, width) or prep.dtype != torch.float32 or state.dtype != torch.float32 or state.dim() != 2:
         raise KernelError("delta_prepare: prep is 32-bit [rows, 2 G dim + H vdim + H + H dim], the state 32-bit [slots, words]", code="invalid_shape")
-    if decay_in.shape != (tokens, heads * dim) or decay_in.dtype != rows.dtype or tuple(taps.shape)[0] != channels or taps.dtype != torch.float32:
-        raise KernelError("delta_prepare: decay_in [rows, H dim] of the rows' dtype, taps 32-bit [channels, n]", code="invalid_shape")
-    if a_log.dtype != torch.float32 or dt_bias.dtype != torch.float32 or a_log.numel() != heads or dt_bias.numel() != heads * dim or rows.stride(1) != 1:
-        raise KernelError("delta_prepare: a_log [H] and dt_bias [H dim] are 32-bit", code="invalid_shape")
-    _check(delta_rule_library().tlie_delta_prepare(_code(rows), c_void_p(rows.data_ptr()), c_int(rows.stride(0)), c_int(beta_offset), _ptr(decay_in), _ptr(taps), _ptr(a_log),
-                                                   _ptr(dt_bias), _ptr(state), c_longlong(state.shape[1]), c_longlong(conv_offset), _i32(ctx.token_seq, "token_seq"),
+    if decay_in.shape != (tokens, decays) or decay_in.dtype != rows.dtype or decay_in.stride(1) != 1 or tuple(taps.shape)[0] != channels or taps.dtype != torch.float32:
+        raise KernelError("delta_prepare: decay_in [rows, H dim] (or [rows, H]) of the rows' dtype, taps 32-bit [channels, n]", code="invalid_shape")
+    if a_log.dtype != torch.float32 or dt_bias.dtype != torch.float32 or a_log.numel() != heads or dt_bias.numel() != decays or rows.stride(1) != 1:
+        raise KernelError("delta_prepare: a_log [H] and dt_bias [H dim] (or [H]) are 32-bit", code="invalid_shape")
+    state_ptr, state_stride = _state_rows(state, "delta_prepare")
+    _check(delta_rule_library().tlie_delta_prepare(_code(rows), c_void_p(rows.data_ptr()), c_int(rows.stride(0)), c_int(beta_offset), c_void_p(decay_in.data_ptr()),
+                                                   c_longlong(decay_in.stride(0)), c_int(1 if decay_per_head else 0), _ptr(taps), _ptr(a_log),
+                                                   _ptr(dt_bias), state_ptr, state_stride, c_longlong(conv_offset), _i32(ctx.token_seq, "token_seq"),
                                                    _i32(ctx.seq_starts, "seq_starts"), _i32(ctx.state_slots, "state_slots"), _ptr(prep), c_int(tokens), c_int(ctx.num_seqs),
                                                    c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(taps.shape[1]), c_float(unit_eps), c_float(q_scale), _stream()),
            "delta_prepare")
 
 
-def delta_rule(prep, state, ctx, out, heads: int, kv_heads: int, dim: int, vdim: int) -> None:
+def delta_rule(prep, state, ctx, out, heads: int, kv_heads: int, dim: int, vdim: int, plain: bool = False) -> None:
     """The gated delta rule over every entry's rows in order, from and into the entries' state slots: per head
-    S <- diag(decay) S; u = beta (v - S^T k); S <- S + k u^T; out = S^T q.  ``out`` is 32-bit [T, heads * vdim]."""
+    S <- diag(decay) S; u = beta (v - S^T k); S <- S + k u^T; out = S^T q.  ``out`` is 32-bit [T, heads * vdim].
+    ``plain``: u = beta v, the recurrence of linear attention with a decay (nothing is taken back before the write).
+    ``prep`` rows are [q: kv_heads dim | k: kv_heads dim | v: heads vdim | beta: heads | decay: heads dim]."""
     tokens = prep.shape[0]
-    if out.shape != (tokens, heads * vdim) or out.dtype != torch.float32 or prep.dtype != torch.float32 or state.dtype != torch.float32:
-        raise KernelError("delta_rule: prep, state and out [rows, H vdim] are 32-bit", code="invalid_shape")
-    _check(delta_rule_library().tlie_delta_rule(_ptr(prep), _ptr(state), c_longlong(state.shape[1]), _i32(ctx.seq_starts, "seq_starts"), _i32(ctx.state_slots, "state_slots"),
-                                                _ptr(out), c_int(ctx.num_seqs), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), _stream()), "delta_rule")
+    if out.shape != (tokens, heads * vdim) or out.dtype != torch.float32 or prep.dtype != torch.float32 or prep.shape[1] != 2 * kv_heads * dim + heads * (vdim + 1 + dim):
+        raise KernelError("delta_rule: prep [rows, 2 G dim + H vdim + H + H dim] and out [rows, H vdim] are 32-bit", code="invalid_shape")
+    state_ptr, state_stride = _state_rows(state, "delta_rule")
+    _check(delta_rule_library().tlie_delta_rule(_ptr(prep), state_ptr, state_stride, _i32(ctx.seq_starts, "seq_starts"), _i32(ctx.state_slots, "state_slots"),
+                                                _ptr(out), c_int(ctx.num_seqs), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(1 if plain else 0), _stream()),
+           "delta_rule")
 
 
-def delta_gate_norm(o, gate, weight, out, eps: float, heads: int, vdim: int) -> None:
-    """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * sigmoid(gate[t, h]) per head (``weight`` [vdim] shared by the heads)."""
+HEAD_GATES = {"sigmoid": 0, "silu": 1, None: 2}
+
+
+def delta_gate_norm(o, gate, weight, out, eps: float, heads: int, vdim: int, gate_kind: str | None = "sigmoid") -> None:
+    """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * act(gate[t, h]) per head (``weight`` [vdim] shared by the heads);
+    ``gate_kind``: "sigmoid", "silu", or None for no gate (``gate`` is then not read)."""
     tokens = o.shape[0]
-    if o.dtype != torch.float32 or weight.dtype != torch.float32 or weight.numel() != vdim or gate.shape != (tokens, heads * vdim) or out.shape != gate.shape or gate.dtype != out.dtype:
-        raise KernelError("delta_gate_norm: o 32-bit [rows, H vdim], weight 32-bit [vdim], gate and out of one dtype and o's shape", code="invalid_shape")
-    _check(delta_rule_library().tlie_delta_gate_norm(_code(out), _ptr(o), _ptr(gate), _ptr(weight), _ptr(out), c_float(eps), c_int(tokens), c_int(heads), c_int(vdim), _stream()),
-           "delta_gate_norm")
+    if gate_kind not in HEAD_GATES:
+        raise KernelError(f"delta_gate_norm: no gate {gate_kind!r}", code="invalid_argument")
+    if o.dtype != torch.float32 or weight.dtype != torch.float32 or weight.numel() != vdim or out.shape != (tokens, heads * vdim):
+        raise KernelError("delta_gate_norm: o 32-bit [rows, H vdim], weight 32-bit [vdim], out of o's shape", code="invalid_shape")
+    if gate_kind is not None and (gate.shape != out.shape or gate.dtype != out.dtype or gate.stride(1) != 1 or not gate.is_cuda):
+        raise KernelError("delta_gate_norm: gate and out are of one dtype and shape (the gate may be a run of columns of wider rows)", code="invalid_shape")
+    gate_ptr, gate_stride = (c_void_p(0), 0) if gate_kind is None else (c_void_p(gate.data_ptr()), gate.stride(0))
+    _check(delta_rule_library().tlie_delta_gate_norm(_code(out), _ptr(o), gate_ptr, c_longlong(gate_stride), _ptr(weight), _ptr(out), c_float(eps), c_int(tokens),
+                                                     c_int(heads), c_int(vdim), c_int(HEAD_GATES[gate_kind]), _stream()), "delta_gate_norm")
+
+
+def hgrn2_prepare(rows, f_bias, lower, prep, heads: int, dim: int, vdim: int) -> None:
+    """What the plain recurrence reads for a mixer whose forget gate also writes: ``rows`` = [q: H dim | f: H dim | v: H vdim] (products);
+    ``prep[t]`` = [silu(q) | 1 - f | v | 1 | f] with f = lower + (1 - lower) sigmoid(f + f_bias), all 32-bit (``f_bias`` may be None)."""
+    tokens = rows.shape[0]
+    if rows.shape[1] < 2 * heads * dim + heads * vdim or rows.stride(1) != 1 or prep.dtype != torch.float32 or prep.shape != (tokens, 3 * heads * dim + heads * vdim + heads):
+        raise KernelError("hgrn2_prepare: rows [T, >= 2 H dim + H vdim], prep 32-bit [T, 3 H dim + H vdim + H]", code="invalid_shape")
+    if lower.dtype != torch.float32 or lower.numel() != heads * dim or (f_bias is not None and (f_bias.dtype != torch.float32 or f_bias.numel() != heads * dim)):
+        raise KernelError("hgrn2_prepare: the lower bound and the bias are 32-bit [H dim]", code="invalid_shape")
+    _check(delta_rule_library().tlie_hgrn2_prepare(_code(rows), c_void_p(rows.data_ptr()), c_int(rows.stride(0)), _ptr(f_bias), _ptr(lower), _ptr(prep), c_int(tokens),
+                                                   c_int(heads), c_int(dim), c_int(vdim), _stream()), "hgrn2_prepare")
+
+
+def ssd_prepare(rows, taps, conv_bias, a_log, dt_bias, state, conv_offset: int, ctx, prep, heads: int, groups: int, n: int, vdim: int) -> None:
+    """What the plain recurrence reads for a state-space layer: ``rows`` = [z: inner | x: inner | B: G n | C: G n | dt: H] (products, inner = H vdim).
+    x, B, C pass a causal convolution per channel (``taps`` 32-bit [inner + 2 G n, taps], ``conv_bias`` or None; the inputs before an entry's first row
+    are read from the request's state at ``conv_offset``, which is moved on afterwards) and silu; dt = softplus(dt + dt_bias);
+    ``prep[t]`` = [C | B | x | dt | exp(-exp(a_log[h]) dt) for the n channels of head h], all 32-bit."""
+    tokens = rows.shape[0]
+    inner, channels = heads * vdim, heads * vdim + 2 * groups * n
+    if rows.shape[1] != inner + channels + heads or rows.stride(1) != 1 or prep.dtype != torch.float32 or prep.shape != (tokens, 2 * groups * n + inner + heads + heads * n):
+        raise KernelError("ssd_prepare: rows [T, 2 inner + 2 G n + H], prep 32-bit [T, 2 G n + inner + H + H n]", code="invalid_shape")
+    if taps.dtype != torch.float32 or taps.shape[0] != channels or a_log.dtype != torch.float32 or a_log.numel() != heads or dt_bias.dtype != torch.float32 or dt_bias.numel() != heads:
+        raise KernelError("ssd_prepare: taps 32-bit [channels, n]; a_log and dt_bias 32-bit [H]", code="invalid_shape")
+    state_ptr, state_stride = _state_rows(state, "ssd_prepare")
+    _check(delta_rule_library().tlie_ssd_prepare(_code(rows), c_void_p(rows.data_ptr()), c_int(rows.stride(0)), _ptr(taps), _ptr(conv_bias), _ptr(a_log), _ptr(dt_bias), state_ptr,
+                                                 state_stride, c_longlong(conv_offset), _i32(ctx.token_seq, "token_seq"), _i32(ctx.seq_starts, "seq_starts"),
+                                                 _i32(ctx.state_slots, "state_slots"), _ptr(prep), c_int(tokens), c_int(ctx.num_seqs), c_int(heads), c_int(groups), c_int(n),
+                                                 c_int(vdim), c_int(taps.shape[1]), _stream()), "ssd_prepare")
+
+
+def ssd_finish(read, prep, x_offset: int, rows, skip, weight, out, eps: float, heads: int, vdim: int, norm_groups: int) -> None:
+    """out = norm((read + skip[h] x) silu(z)) * weight: ``read`` 32-bit [T, H vdim] is the recurrence's output, x the value columns of ``prep`` (from
+    ``x_offset``), z the first H vdim columns of ``rows``; the RMS norm runs over each of ``norm_groups`` equal parts of a row (``eps`` inside the root)."""
+    tokens, inner = read.shape[0], heads * vdim
+    if read.dtype != torch.float32 or read.shape != (tokens, inner) or prep.dtype != torch.float32 or out.shape != (tokens, inner) or out.dtype != rows.dtype or rows.stride(1) != 1:
+        raise KernelError("ssd_finish: read and prep are 32-bit, out [T, H vdim] of the rows' dtype", code="invalid_shape")
+    if skip.dtype != torch.float32 or skip.numel() != heads or weight.dtype != torch.float32 or weight.numel() != inner or inner % norm_groups:
+        raise KernelError("ssd_finish: skip 32-bit [H], weight 32-bit [H vdim], norm_groups a divisor of H vdim", code="invalid_shape")
+    _check(delta_rule_library().tlie_ssd_finish(_code(out), _ptr(read), _ptr(prep), c_int(prep.shape[1]), c_int(x_offset), c_void_p(rows.data_ptr()), c_int(rows.stride(0)),
+                                                _ptr(skip), _ptr(weight), _ptr(out), c_float(eps), c_int(tokens), c_int(heads), c_int(vdim), c_int(norm_groups), _stream()),
+           "ssd_finish")
+
+
+# --- what looks back along a request ---------------------------------------------------------------
+def sequence_library():
+    return load_library("tlie_sequence", SEQUENCE_SOURCES)
+
+
+def pair_embedding(table, pairs, ctx, state, state_offset: int, weight, eps: float, scale: float, residual, buckets: int, mul_prev: int, mul_cur: int, groups: int) -> None:
+    """residual[t] = norm(table[id_t] * scale + pairs[(id_{t-1} mul_prev + id_t mul_cur) mod buckets]) in 32-bit: a second table's row chosen by the token
+    and the one before it (row ``buckets`` for a request's first token).  The token before a step's first row of a request is the word
+    ``state_offset`` of the request's state (the id's bits), renewed after the step.  ``pairs`` None: no second table; ``weight`` None: no norm;
+    the norm is an RMS norm over each of ``groups`` equal parts of a row."""
+    rows, width = residual.shape
+    if residual.dtype != torch.float32 or table.shape[1] != width or (pairs is not None and (pairs.shape != (buckets + 1, width) or pairs.dtype != table.dtype)):
+        raise KernelError("pair_embedding: a 32-bit residual [T, width], a table [vocab, width], pairs [buckets + 1, width] of the table's dtype", code="invalid_shape")
+    if weight is not None and (weight.dtype != torch.float32 or weight.numel() != width):
+        raise KernelError("pair_embedding: the norm weight is 32-bit [width]", code="invalid_shape")
+    state_ptr, state_stride = (c_void_p(0), c_longlong(0)) if pairs is None else _state_rows(state, "pair_embedding")
+    _check(sequence_library().tlie_pair_embedding(_code(table), _ptr(table), _ptr(pairs), _i32(ctx.token_ids, "ids"), _i32(ctx.positions, "positions"),
+                                                  _i32(ctx.token_seq, "token_seq"), _i32(ctx.seq_starts, "seq_starts"), _i32(ctx.state_slots, "state_slots"), state_ptr,
+                                                  state_stride, c_longlong(state_offset), _ptr(weight), c_float(eps), c_float(scale), _ptr(residual), c_int(rows),
+                                                  c_int(ctx.num_seqs), c_int(width), c_int(table.shape[0]), c_int(buckets), c_longlong(mul_prev), c_longlong(mul_cur),
+                                                  c_int(groups), _ptr(error_flag(residual.device)), _stream()), "pair_embedding")
+
+
+def conv_residual(x, taps, state, state_offset: int, ctx, out) -> None:
+    """out[t, c] = x[t, c] + sum_j taps[c, j] x[t - n + 1 + j, c] along every request (zeros before its start), 32-bit inside.  The n - 1 inputs
+    before a step's first row of a request are read from the request's state at ``state_offset`` ([n - 1, channels]), which is moved on afterwards."""
+    rows, channels = x.shape
+    if out.shape != x.shape or out.dtype != x.dtype or out.data_ptr() == x.data_ptr() or taps.dtype != torch.float32 or taps.shape[0] != channels:
+        raise KernelError("conv_residual: out has x's shape and dtype and is another buffer; taps are 32-bit [channels, n]", code="invalid_shape")
+    state_ptr, state_stride = (c_void_p(0), c_longlong(0)) if taps.shape[1] == 1 else _state_rows(state, "conv_residual")
+    _check(sequence_library().tlie_conv_residual(_code(x), _ptr(x), _ptr(taps), state_ptr, state_stride, c_longlong(state_offset), _i32(ctx.token_seq, "token_seq"),
+                                                 _i32(ctx.seq_starts, "seq_starts"), _i32(ctx.state_slots, "state_slots"), _ptr(out), c_int(rows), c_int(ctx.num_seqs),
+                                                 c_int(channels), c_int(taps.shape[1]), _stream()), "conv_residual")
+
+
+def add_bias(x, bias) -> None:
+    """x[t, c] += bias[c] in place (``bias`` 32-bit [width]), 32-bit inside."""
+    if bias.dtype != torch.float32 or x.dim() != 2 or bias.numel() != x.shape[1]:
+        raise KernelError("add_bias: x [rows, width], bias 32-bit [width]", code="invalid_shape")
+    _check(sequence_library().tlie_add_bias(_code(x), _ptr(x), _ptr(bias), c_int(x.shape[0]), c_int(x.shape[1]), _stream()), "add_bias")
+
+
+def scaled_sum(x, y, a: float, b: float, out) -> None:
+    """out = a x + b y, 32-bit inside (``out`` may be ``x`` or ``y``)."""
+    if x.shape != y.shape or out.shape != x.shape or x.dtype != y.dtype or out.dtype != x.dtype:
+        raise KernelError("scaled_sum: x, y and out share a shape and a dtype", code="invalid_shape")
+    _check(sequence_library().tlie_scaled_sum(_code(x), _ptr(x), _ptr(y), c_float(a), c_float(b), _ptr(out), c_longlong(x.numel()), _stream()), "scaled_sum")
 
 
 # --- attention with mixed heads --------------------------------------------------------------
@@ -687,6 +808,26 @@ def store_kv_planes(rows, k_offset: int, v_offset: int, positions, token_seq, ca
                                                   _i32(token_seq, "token_seq"), _i32(table, "block_table"), c_int(table.shape[1]), k_ptr, c_longlong(k_stride),
                                                   v_ptr, c_longlong(v_stride), c_int(rows.shape[0]), c_int(kv_heads), c_int(key_dim), c_int(value_dim),
                                                   c_int(cache.page_size), _stream()), "store_kv_planes")
+
+
+def rotary_store_planes(rows, k_offset: int, v_offset: int, biases, inv_freq, rot_dims: int, positions, token_seq, cache, heads: int, kv_heads: int, key_dim: int,
+                        value_dim: int) -> None:
+    """Biases, a partial rotation and the cache write in one kernel: every q, k and v vector of ``rows`` gets its bias (``biases`` = (q, k, v), 32-bit
+    or None each); of every q and k head the first ``rot_dims`` columns turn, column i with column i + rot_dims / 2, by position * inv_freq[i];
+    q is left in place, k goes into the key plane and v into the value plane of the token's page."""
+    pages, k_ptr, k_stride, v_ptr, v_stride = _plane_pointers(cache, kv_heads, key_dim, value_dim)
+    if pages.dtype != rows.dtype or rot_dims % 2 or rot_dims > key_dim or (rot_dims > 0 and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dims // 2)):
+        raise KernelError("rotary_store_planes: pages of the rows' dtype; inv_freq 32-bit [rot_dims / 2], rot_dims even and at most key_dim", code="invalid_shape")
+    q_bias, k_bias, v_bias = biases if biases is not None else (None, None, None)
+    for bias, count in ((q_bias, heads * key_dim), (k_bias, kv_heads * key_dim), (v_bias, kv_heads * value_dim)):
+        if bias is not None and (bias.dtype != torch.float32 or bias.numel() != count):
+            raise KernelError("rotary_store_planes: biases are 32-bit, one number per column", code="invalid_shape")
+    table = cache.block_table
+    _check(mixed_attention().tlie_rotary_store_planes(_code(rows), _ptr(rows), c_int(rows.shape[1]), c_int(k_offset), c_int(v_offset), _ptr(q_bias), _ptr(k_bias), _ptr(v_bias),
+                                                      _ptr(inv_freq if rot_dims > 0 else None), c_int(rot_dims), _i32(positions, "positions"), _i32(token_seq, "token_seq"),
+                                                      _i32(table, "block_table"), c_int(table.shape[1]), k_ptr, c_longlong(k_stride), v_ptr, c_longlong(v_stride),
+                                                      c_int(rows.shape[0]), c_int(heads), c_int(kv_heads), c_int(key_dim), c_int(value_dim), c_int(cache.page_size),
+                                                      c_int(1 if cache.writes else 0), _stream()), "rotary_store_planes")
 
 
 def mixed_heads_attention(rows, gate_offset: int, positions, token_seq, cache, slopes, mix, out, heads: int, kv_heads: int, key_dim: int, value_dim: int,
@@ -824,11 +965,12 @@ def moe_library():
     return load_library("tlie_moe", MOE_SOURCES)
 
 
-def moe_route(x, router, correction, ids, weights, groups: int, keep: int, route_scale: float) -> None:
+def moe_route(x, router, correction, ids, weights, groups: int, keep: int, route_scale: float, normalize: bool = True) -> None:
     """Per token of ``x`` [T, width]: s = sigmoid(router x) (``router`` 32-bit [experts, width], sums in 32-bit), choice = s + ``correction``
     (32-bit [experts] or None).  Experts form ``groups`` equal groups of neighbours; a group's score is the sum of its two largest choice
     scores and only experts of the ``keep`` best groups can be chosen.  ``ids`` int32 [T, top] receives the experts of the ``top`` largest
-    choice scores (the lower index on ties), ``weights`` 32-bit [T, top] their s / (sum of the chosen s + 1e-20) * ``route_scale``."""
+    choice scores (the lower index on ties), ``weights`` 32-bit [T, top] their s / (sum of the chosen s + 1e-20) * ``route_scale``
+    (``normalize`` False: s * ``route_scale``, the scores as they are)."""
     tokens, width = x.shape
     experts, top = router.shape[0], ids.shape[1]
     if router.dtype != torch.float32 or router.shape[1] != width or ids.dtype != torch.int32 or ids.shape != (tokens, top) or weights.dtype != torch.float32 or weights.shape != (tokens, top):
@@ -836,14 +978,15 @@ def moe_route(x, router, correction, ids, weights, groups: int, keep: int, route
     if correction is not None and (correction.dtype != torch.float32 or correction.numel() != experts):
         raise KernelError("moe_route: the correction is 32-bit [experts]", code="invalid_shape")
     _check(moe_library().tlie_moe_route(_code(x), _ptr(x), _ptr(router), _ptr(correction), _ptr(ids), _ptr(weights), c_int(tokens), c_int(width), c_int(experts),
-                                        c_int(groups), c_int(keep), c_int(top), c_float(route_scale), _stream()), "moe_route")
+                                        c_int(groups), c_int(keep), c_int(top), c_float(route_scale), c_int(1 if normalize else 0), _stream()), "moe_route")
 
 
-def moe_experts(x, gate_up, down, ids, weights, shared, out, activation: str = "silu", batch=None) -> None:
+def moe_experts(x, gate_up, down, ids, weights, shared, out, activation: str = "silu", batch=None, weight_input: bool = False) -> None:
     """out[t] = sum_k weights[t, k] * W_down[e] (act(W_gate[e] x[t]) * (W_up[e] x[t])) for e = ids[t, k], plus ``shared[t]`` if given.
     ``gate_up`` [experts, 2 ff, width] (an expert's gate rows, then its up rows), ``down`` [experts, width, ff].  Steps of few rows and the
     32-bit path read each chosen expert's rows directly; bfloat16 prompt portions sort the (token, expert) pairs by expert and run
-    the experts' products on the tensor cores."""
+    the experts' products on the tensor cores.  ``weight_input``: the weight multiplies what the expert reads instead of what it returns,
+    out[t] = sum_k expert_e(weights[t, k] x[t]) (the two differ: the experts are not linear)."""
     tokens, width = x.shape
     experts, two_ff, _ = gate_up.shape
     ff, top = two_ff // 2, ids.shape[1]
@@ -853,12 +996,12 @@ def moe_experts(x, gate_up, down, ids, weights, shared, out, activation: str = "
         raise KernelError("moe_experts: the shared branch has the output's shape and dtype", code="invalid_shape")
     if activation not in GATE_KINDS:
         raise KernelError(f"moe_experts: no activation {activation!r}", code="invalid_argument")
-    if x.dtype == torch.bfloat16 and fast.moe_grouped_takes(tokens, top, width, ff, experts):
+    if x.dtype == torch.bfloat16 and not weight_input and fast.moe_grouped_takes(tokens, top, width, ff, experts):
         fast.moe_grouped(x, gate_up, down, ids, weights, shared, out, GATE_KINDS[activation])
         return
     act = fast.mixed_scratch(x.device, tokens * top * ff, x.dtype)
     _check(moe_library().tlie_moe_experts(_code(x), _ptr(x), _ptr(gate_up), _ptr(down), _ptr(ids), _ptr(weights), _ptr(shared), _ptr(act), _ptr(out), c_int(tokens),
-                                          c_int(width), c_int(ff), c_int(top), c_int(GATE_KINDS[activation]), _stream()), "moe_experts")
+                                          c_int(width), c_int(ff), c_int(top), c_int(GATE_KINDS[activation]), c_int(1 if weight_input else 0), _stream()), "moe_experts")
 
 
 # --- sampling ------------------------------------------------------------------------------

@@ -99,9 +99,11 @@ class MixedHeadsAttention(Mixer):
     params: ``hidden_size``, ``num_heads``, ``num_kv_heads`` (query head h reads key/value head h // (heads / kv heads)),
     ``key_dim`` (queries and keys), ``value_dim``, ``scale``, ``window`` (0: every earlier token), ``distance_slopes``
     (one slope per head, or None for no bias), ``mix_heads`` (tensor ``<prefix>.talk`` [heads, heads], row h mixing into head h),
-    ``output_gate`` (tensor ``<prefix>.g`` [heads * value_dim, hidden]).
+    ``output_gate`` (tensor ``<prefix>.g`` [heads * value_dim, hidden]); optional ``biases`` (q, k, v and the output projection have one each, the
+    tensor's name with ``.b`` added, added in 32-bit) and ``rot_dims`` / ``rot_base`` (of every q and k head the first ``rot_dims`` columns turn, column i
+    with column i + rot_dims / 2, by position * rot_base^(-2i / rot_dims); keys are cached turned).
     tensors: ``<prefix>.q`` [heads * key_dim, hidden], ``<prefix>.k`` [kv * key_dim, hidden], ``<prefix>.v`` [kv * value_dim, hidden],
-    ``<prefix>.o`` [hidden, heads * value_dim]; no biases.  q, k, v and the gate are one stacked product.  Keys and values are
+    ``<prefix>.o`` [hidden, heads * value_dim].  q, k, v and the gate are one stacked product.  Keys and values are
     two planes of a page (of different widths if ``key_dim != value_dim``); scores, mix, softmax and the gate are 32-bit.
     """
 
@@ -124,7 +126,11 @@ class MixedHeadsAttention(Mixer):
             specs.append(TensorSpec(f"{prefix}.talk", (heads, heads), std=heads ** -0.5))
         if spec.get("output_gate"):
             specs.append(TensorSpec(f"{prefix}.g", (heads * value_dim, hidden), std=std))
-        return specs + [TensorSpec(f"{prefix}.o", (hidden, heads * value_dim), std=(heads * value_dim) ** -0.5)]
+        specs.append(TensorSpec(f"{prefix}.o", (hidden, heads * value_dim), std=(heads * value_dim) ** -0.5))
+        if spec.get("biases"):
+            specs += [TensorSpec(f"{prefix}.q.b", (heads * key_dim,), std=0.5), TensorSpec(f"{prefix}.k.b", (kv * key_dim,), std=0.5),
+                      TensorSpec(f"{prefix}.v.b", (kv * value_dim,), std=0.5), TensorSpec(f"{prefix}.o.b", (hidden,), std=0.5)]
+        return specs
 
     @classmethod
     def cache_need(cls, spec: PartSpec) -> CacheNeed:
@@ -150,9 +156,22 @@ class MixedHeadsAttention(Mixer):
         self.slopes = None if slopes is None else torch.tensor([float(v) for v in slopes], dtype=torch.float32, device=runtime.device)
         self.mix = weights.get(f"{prefix}.talk", torch.float32).contiguous() if spec.get("mix_heads") else None
         self.folded_slopes = ops.fast.folded_slopes(self.slopes, self.mix) if self.slopes is not None and self.slopes.is_cuda else None
+        self.biases = self.out_bias = None
+        if spec.get("biases"):
+            self.biases = tuple(weights.get(f"{prefix}.{n}.b", torch.float32).contiguous() for n in ("q", "k", "v"))
+            self.out_bias = weights.get(f"{prefix}.o.b", torch.float32).contiguous()
+        self.rot_dims = int(spec.get("rot_dims", 0) or 0)
+        self.inv_freq = None
+        if self.rot_dims:
+            # frequencies in 64-bit, rounded once: the angle is float(position) * frequency in 32-bit inside the kernel
+            exponent = -2.0 * np.arange(self.rot_dims // 2, dtype=np.float64) / float(self.rot_dims)
+            self.inv_freq = torch.from_numpy(np.power(float(spec["rot_base"]), exponent).astype(np.float32)).to(runtime.device)
+        if self.biases is not None or self.rot_dims:
+            # the kernels of few rows take neither: such a layer is handed finished tensors and returns its output
+            self.accepts_lazy_norm = self.fuses_residual_add = self.prepares_next_norm = False
 
     def adds_to_residual(self, rows: int) -> bool:
-        return ops.can_accumulate(rows, self.w_o)
+        return self.out_bias is None and ops.can_accumulate(rows, self.w_o)
 
     def forward(self, x, ctx, cache: LayerCache, accumulate_into=None, prepare=None):
         ws, dtype, tokens = self.runtime.workspace, self.runtime.dtype, x.shape[0]
@@ -161,7 +180,10 @@ class MixedHeadsAttention(Mixer):
             ops.norm_linear(x, self.w_in, rows)
         else:
             ops.linear(x, self.w_in, rows)
-        if cache.writes:
+        if self.biases is not None or self.rot_dims:
+            ops.rotary_store_planes(rows, self.k_offset, self.v_offset, self.biases, self.inv_freq, self.rot_dims, ctx.positions, ctx.token_seq, cache, self.heads,
+                                    self.kv_heads, self.key_dim, self.value_dim)
+        elif cache.writes:
             ops.store_kv_planes(rows, self.k_offset, self.v_offset, ctx.positions, ctx.token_seq, cache, self.kv_heads, self.key_dim, self.value_dim)
         mixed = ws.get("attention", tokens, self.heads * self.value_dim, dtype)
         ops.mixed_heads_attention(rows, self.gate_offset, ctx.positions, ctx.token_seq, cache, self.slopes, self.mix, mixed, self.heads, self.kv_heads,
@@ -171,6 +193,8 @@ class MixedHeadsAttention(Mixer):
             return None
         out = ws.get("mixer_out", tokens, self.hidden, dtype)
         ops.linear(mixed, self.w_o, out)
+        if self.out_bias is not None:
+            ops.add_bias(out, self.out_bias)
         return out
 
 

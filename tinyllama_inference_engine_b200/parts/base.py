@@ -50,6 +50,9 @@ class CacheNeed:
     would be a single plane, keys and values of different widths two unequal ones.
     kind "state": one tensor of ``state_shape`` per request (always 32-bit).
     kind "none": nothing.
+    A need of kind "pages" may name a ``state_shape`` as well (a layer that keeps keys and values and, beside them, a state of
+    fixed size: a recurrent mixer next to the attention, the last inputs of a short convolution); its stream then belongs to
+    a page group and to a state group.
     """
 
     kind: str = "none"
@@ -72,6 +75,35 @@ class CacheNeed:
 
     def group_key(self) -> tuple:
         return (self.kind, self.page_planes(), self.window, self.state_shape, self.keep_first if self.window > 0 else 0)
+
+    def page_key(self) -> tuple | None:
+        """What streams of one page group agree in (None: the need has no pages)."""
+        if self.kind != "pages":
+            return None
+        return (self.page_planes(), self.window, self.keep_first if self.window > 0 else 0)
+
+    def state_key(self) -> tuple | None:
+        """What streams of one state group agree in (None: the need has no state)."""
+        if self.kind not in ("pages", "state") or not self.state_shape:
+            return None
+        return tuple(int(n) for n in self.state_shape)
+
+    def with_state(self, words: int) -> "CacheNeed":
+        """This need with ``words`` more 32-bit words of per-request state behind its own (a flat state: one axis)."""
+        from dataclasses import replace
+
+        if words <= 0:
+            return self
+        if self.state_shape and len(self.state_shape) != 1:
+            raise ConfigError("only a flat per-request state can be extended")
+        held = int(self.state_shape[0]) if self.state_shape else 0
+        return replace(self, kind="state" if self.kind == "none" else self.kind, state_shape=(held + int(words),))
+
+    def state_words(self) -> int:
+        count = 1
+        for n in self.state_shape:
+            count *= int(n)
+        return count if self.state_shape else 0
 
 
 @dataclass
@@ -203,6 +235,20 @@ class TokenInput(Part):
         raise NotImplementedError
 
 
+class InputFilter(Part):
+    """Something between a norm and the sublayer that reads it, along the rows of a request: ``forward(x, ctx, state, offset) -> y`` of x's shape.
+    ``state_words(spec)``: the 32-bit words it keeps per request between steps (they lie at ``offset`` of ``state`` [slots, words])."""
+
+    category = "input_filter"
+
+    @classmethod
+    def state_words(cls, spec: PartSpec) -> int:
+        return 0
+
+    def forward(self, x, ctx, state, offset: int):
+        raise NotImplementedError
+
+
 class Block(Part):
     category = "block"
     traced = True                  # False: a run of this block is no layer of its own in a trace of layer outputs
@@ -255,7 +301,7 @@ def norm_then_part(norm, part, residual, pending, fused: bool, next_norm, *args)
 
 # --- registry of part classes -------------------------------------------------------------
 _PARTS: dict[tuple[str, str], type] = {}
-CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head", "token_input")
+CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head", "token_input", "input_filter")
 
 
 def register_part(category: str, kind: str, cls: type, *, replace: bool = False) -> None:

@@ -101,20 +101,24 @@ class SandwichNormBlock(Block):
 
     params: ``mixer``, ``feed_forward`` (or None), and the four norms ``mixer_norm``, ``mixer_post_norm``, ``feed_forward_norm``,
     ``feed_forward_post_norm`` (PartSpecs of a norm kind that offers ``join``), each with its tensor-name suffix (``*_name``).
+    Optional ``mixer_filter`` / ``feed_forward_filter`` (PartSpecs of category ``input_filter``, with ``*_name``): what stands between a
+    sublayer's first norm and the sublayer (a short convolution over time); what they keep per request lies behind the mixer's own
+    state in the layer's state.
     A branch's norm, its sum into the 32-bit stream and the norm that reads the stream next are one kernel (``Norm.join``); the norm
     that follows the block's last sublayer is the next block's first one, which the block is told (``next_norm``) and hands over
     finished, as a prepared norm, if it is of the same kind.
     """
 
-    _SLOTS = (("mixer_norm", "norm"), ("mixer", "mixer"), ("mixer_post_norm", "norm"), ("feed_forward_norm", "norm"), ("feed_forward", "feed_forward"),
-              ("feed_forward_post_norm", "norm"))
+    _SLOTS = (("mixer_norm", "norm"), ("mixer_filter", "input_filter"), ("mixer", "mixer"), ("mixer_post_norm", "norm"), ("feed_forward_norm", "norm"),
+              ("feed_forward_filter", "input_filter"), ("feed_forward", "feed_forward"), ("feed_forward_post_norm", "norm"))
 
     capturable = True
     accepts_next_norm = True
 
     @classmethod
     def _slots(cls, spec: PartSpec):
-        return [pair for pair in cls._SLOTS if spec.get("feed_forward") is not None or not pair[0].startswith("feed_forward")]
+        slots = [pair for pair in cls._SLOTS if spec.get("feed_forward") is not None or not pair[0].startswith("feed_forward")]
+        return [pair for pair in slots if pair[1] != "input_filter" or spec.get(pair[0]) is not None]
 
     @classmethod
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
@@ -125,14 +129,28 @@ class SandwichNormBlock(Block):
         return specs
 
     @classmethod
+    def _filter_words(cls, spec: PartSpec) -> list[int]:
+        return [part_class(category, spec[slot]).state_words(spec[slot]) for slot, category in cls._slots(spec) if category == "input_filter"]
+
+    @classmethod
     def cache_need(cls, spec: PartSpec) -> CacheNeed:
-        return part_class("mixer", spec["mixer"]).cache_need(spec["mixer"])
+        need = part_class("mixer", spec["mixer"]).cache_need(spec["mixer"])
+        return need.with_state(sum(cls._filter_words(spec)))
 
     def __init__(self, spec, prefix, weights, runtime):
         super().__init__(spec, prefix, weights, runtime)
-        self.feed_forward = self.feed_forward_norm = self.feed_forward_post_norm = None
+        self.feed_forward = self.feed_forward_norm = self.feed_forward_post_norm = self.mixer_filter = self.feed_forward_filter = None
         for slot, category in self._slots(spec):
             setattr(self, slot, build_part(category, spec[slot], f"{prefix}.{spec[slot + '_name']}", weights, runtime))
+        # the layer's state: [the mixer's own words | the first filter's | the second filter's]
+        self.mixer_need = part_class("mixer", spec["mixer"]).cache_need(spec["mixer"])
+        self.mixer_words = self.mixer_need.state_words()
+        self.filter_offsets, at = {}, self.mixer_words
+        for slot, category in self._slots(spec):
+            if category == "input_filter":
+                self.filter_offsets[slot] = at
+                at += part_class(category, spec[slot]).state_words(spec[slot])
+        self.filtered = at > self.mixer_words
 
     @property
     def first_norm(self):
@@ -140,7 +158,15 @@ class SandwichNormBlock(Block):
 
     @staticmethod
     def _joinable(norm, following) -> bool:
-        return following is not None and type(following) is type(norm) and following.eps == norm.eps and following.size == norm.size
+        return (following is not None and type(following) is type(norm) and following.eps == norm.eps and following.size == norm.size
+                and getattr(following, "groups", 1) == getattr(norm, "groups", 1))
+
+    def _mixer_cache(self, cache: LayerCache) -> LayerCache:
+        """The layer's cache as the mixer declared it: without the words the filters keep behind the mixer's."""
+        if not self.filtered:
+            return cache
+        state = cache.state[:, : self.mixer_words] if self.mixer_words else None
+        return LayerCache(self.mixer_need, cache.writes, cache.pages, cache.block_table, cache.page_size, state, cache.plane_pages)
 
     def forward(self, residual, pending, ctx, cache: LayerCache, next_norm=None):
         from .. import ops
@@ -149,10 +175,14 @@ class SandwichNormBlock(Block):
             x = pending.prepared[0]   # the block before left this block's first norm finished
         else:
             x = self.mixer_norm.forward(residual, None if isinstance(pending, ops.LazyNorm) else pending)
-        branch = self.mixer.forward(x, ctx, cache)
+        if self.mixer_filter is not None:
+            x = self.mixer_filter.forward(x, ctx, cache.state, self.filter_offsets["mixer_filter"])
+        branch = self.mixer.forward(x, ctx, self._mixer_cache(cache))
         last = self.mixer_post_norm
         if self.feed_forward is not None:
             x = self.mixer_post_norm.join(residual, branch, self.feed_forward_norm)
+            if self.feed_forward_filter is not None:
+                x = self.feed_forward_filter.forward(x, ctx, cache.state, self.filter_offsets["feed_forward_filter"])
             branch = self.feed_forward.forward(x, ctx)
             last = self.feed_forward_post_norm
         if self._joinable(last, next_norm):

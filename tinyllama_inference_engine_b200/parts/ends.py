@@ -78,6 +78,54 @@ class PositionedEmbedding(Part):
         return residual
 
 
+class PairEmbedding(Part):
+    """hidden = norm(table[token] * scale + pairs[(previous token * mul_prev + token * mul_cur) mod buckets]): beside the token's own row a row of
+    a second table chosen by the token and the one before it; a request's first token reads that table's last row (number ``buckets``).
+
+    params: ``vocab_size``, ``hidden_size``, ``tensor`` (the token table's name), optional ``scale`` (1.0), optional ``pairs`` = {``tensor``, ``buckets``,
+    ``mul_prev``, ``mul_cur``} (the second table, [buckets + 1, hidden]), optional ``norm`` = {``tensor``, ``eps``, ``groups``} (an RMS norm of the sum over
+    ``groups`` equal parts of the row).  The token before a step's first row belongs to the request: one word of per-request state, which the
+    cache manager keeps like a mixer's.  Sum, statistics and result are 32-bit: the result is the residual stream.
+    """
+
+    capturable = True
+    category = "embedding"
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
+        hidden = spec["hidden_size"]
+        specs = [TensorSpec(_tensor_name(spec), (spec["vocab_size"], hidden), std=1.0)]
+        if spec.get("pairs"):
+            specs.append(TensorSpec(spec["pairs"]["tensor"], (spec["pairs"]["buckets"] + 1, hidden), std=1.0))
+        if spec.get("norm"):
+            specs.append(TensorSpec(spec["norm"]["tensor"], (hidden,), init="norm", std=0.1))
+        return specs
+
+    @classmethod
+    def cache_need(cls, spec: PartSpec):
+        from .base import CacheNeed
+
+        return CacheNeed("state", state_shape=(1,)) if spec.get("pairs") else CacheNeed()
+
+    def __init__(self, spec, prefix, weights, runtime):
+        super().__init__(spec, prefix, weights, runtime)
+        self.hidden = int(spec["hidden_size"])
+        self.table = weights.get(_tensor_name(spec), runtime.dtype).contiguous()
+        pairs, norm = spec.get("pairs"), spec.get("norm")
+        self.pairs = weights.get(pairs["tensor"], runtime.dtype).contiguous() if pairs else None
+        self.buckets, self.mul_prev, self.mul_cur = (int(pairs[k]) for k in ("buckets", "mul_prev", "mul_cur")) if pairs else (1, 0, 0)
+        self.norm_weight = weights.get(norm["tensor"], torch.float32).contiguous() if norm else None
+        self.eps = float(norm["eps"]) if norm else 0.0
+        self.groups = int(norm.get("groups", 1) or 1) if norm else 1
+        self.scale = float(spec.get("scale", 1.0))
+
+    def forward(self, token_ids, ctx=None, cache=None):
+        residual = self.runtime.workspace.get("residual", token_ids.shape[0], self.hidden, torch.float32)
+        ops.pair_embedding(self.table, self.pairs, ctx, None if cache is None else cache.state, 0, self.norm_weight, self.eps, self.scale, residual,
+                           self.buckets, self.mul_prev, self.mul_cur, self.groups)
+        return residual
+
+
 class LinearHead(Part):
     """logits = W . normed, 32-bit out, for the wanted rows only (src/model.cpp:217-225).
 
@@ -119,4 +167,5 @@ class LinearHead(Part):
 
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("embedding", "positioned_embedding", PositionedEmbedding)
+register_part("embedding", "pair_embedding", PairEmbedding)
 register_part("head", "linear_head", LinearHead)

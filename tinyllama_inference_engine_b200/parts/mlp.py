@@ -157,9 +157,12 @@ class RoutedExperts(FeedForward):
     alone.  Experts form ``groups`` equal groups of neighbours; a group's score is the sum of its two largest choice scores, and only
     experts of the ``keep_groups`` best groups can be chosen.  The ``top`` largest choice scores are chosen; their weights are
     s / (sum of the chosen s + 1e-20) * ``route_scale``.  out = sum_k weight_k expert_k(x) + shared(x).
+    ``normalize`` False: the weights are the chosen experts' scores as they are (times ``route_scale``).  ``weight_input`` True: the weight
+    multiplies what the expert reads and not what it returns, out = sum_k expert_k(weight_k x) + shared(x).
 
     params: ``hidden_size``, ``experts``, ``top``, ``expert_size`` (an expert's inner width), ``groups``, ``keep_groups``, ``route_scale``,
-    ``activation`` ("silu" or "gelu_tanh"), ``shared_size`` (0 or None: no shared expert), ``correction`` (whether the tensor exists).
+    ``activation`` ("silu" or "gelu_tanh"), ``shared_size`` (0 or None: no shared expert), ``correction`` (whether the tensor exists),
+    ``normalize`` (True), ``weight_input`` (False).
     tensors: ``<prefix>.router`` [experts, hidden], ``<prefix>.correction`` [experts], ``<prefix>.e<i>.{gate,up,down}``,
     ``<prefix>.shared.{gate,up,down}``.  The experts' gate and up rows are stacked per expert at load time, [experts, 2 ff, hidden].
     """
@@ -194,6 +197,7 @@ class RoutedExperts(FeedForward):
         self.groups, self.keep = int(spec.get("groups", 1) or 1), int(spec.get("keep_groups", 1) or 1)
         self.route_scale = float(spec.get("route_scale", 1.0))
         self.activation = spec.get("activation", "silu")
+        self.normalize, self.weight_input = bool(spec.get("normalize", True)), bool(spec.get("weight_input", False))
         if self.experts % self.groups or not 0 < self.keep <= self.groups or not 0 < self.top <= self.keep * (self.experts // self.groups):
             raise ConfigError(f"{prefix}: {self.experts} experts in {self.groups} groups of which {self.keep} are kept cannot give {self.top} per token")
         if self.activation not in ops.GATE_KINDS:
@@ -210,10 +214,10 @@ class RoutedExperts(FeedForward):
         ws, dtype, tokens = self.runtime.workspace, self.runtime.dtype, x.shape[0]
         ids = ws.get("expert_ids", tokens, self.top, torch.int32)
         weights = ws.get("expert_weights", tokens, self.top, torch.float32)
-        ops.moe_route(x, self.router, self.correction, ids, weights, self.groups, self.keep, self.route_scale)
+        ops.moe_route(x, self.router, self.correction, ids, weights, self.groups, self.keep, self.route_scale, normalize=self.normalize)
         shared = None if self.shared is None else self.shared.forward(x, ctx)
         out = ws.get("routed_out", tokens, self.hidden, dtype)
-        ops.moe_experts(x, self.w_gate_up, self.w_down, ids, weights, shared, out, self.activation, batch=ctx)
+        ops.moe_experts(x, self.w_gate_up, self.w_down, ids, weights, shared, out, self.activation, batch=ctx, weight_input=self.weight_input)
         return out
 
 

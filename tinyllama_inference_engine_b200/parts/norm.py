@@ -64,6 +64,7 @@ class LayerNorm(Norm):
     capturable = True
     supports_lazy = False
     centred = True
+    groups = 1
 
     @classmethod
     def tensor_specs(cls, spec: PartSpec, prefix: str) -> list[TensorSpec]:
@@ -80,18 +81,41 @@ class LayerNorm(Norm):
             ops.add_(residual, delta)
         count = residual.shape[0] if rows is None else rows.shape[0]
         out = self.runtime.workspace.get("normed" if rows is None else "normed_rows", count, self.size, self.runtime.dtype)
-        ops.branch_norm(residual, None, None, self.weight, out, self.eps, self.centred, rows)
+        ops.branch_norm(residual, None, None, self.weight, out, self.eps, self.centred, rows, groups=self.groups)
         return out
 
     def join(self, residual, branch, following: "LayerNorm | None" = None):
         """``residual += self(branch)``; with ``following`` (a norm of this kind and eps) also returns ``following(residual)``, one kernel."""
         if following is None:
-            ops.branch_norm(residual, branch, self.weight, None, None, self.eps, self.centred)
+            ops.branch_norm(residual, branch, self.weight, None, None, self.eps, self.centred, groups=self.groups)
             return None
         out = self.runtime.workspace.get("normed", residual.shape[0], self.size, self.runtime.dtype)
-        ops.branch_norm(residual, branch, self.weight, following.weight, out, self.eps, self.centred)
+        ops.branch_norm(residual, branch, self.weight, following.weight, out, self.eps, self.centred, groups=self.groups)
         return out
 
 
+class GroupedRMSNorm(LayerNorm):
+    """y = x / sqrt(mean(x^2) + eps) * weight over each of ``groups`` equal consecutive parts of a row, every part with a root mean
+    square of its own (one group: the plain RMS norm).
+
+    params: ``size``, ``eps``, ``groups``, optional ``suffix`` and ``scale`` (the weight is multiplied by it once, in 32-bit, at load time:
+    a branch that joins the stream times a constant).  ``forward`` and ``join`` are the layer norm's: the norm of a branch, its sum
+    into the 32-bit stream and the stream's next norm are one kernel."""
+
+    centred = False
+
+    def __init__(self, spec, prefix, weights, runtime):
+        super().__init__(spec, prefix, weights, runtime)
+        self.groups = int(spec.get("groups", 1) or 1)
+        if self.size % self.groups:
+            from ..errors import ConfigError
+
+            raise ConfigError(f"{prefix}: a norm over {self.size} columns cannot have {self.groups} equal groups")
+        scale = float(spec.get("scale", 1.0))
+        if scale != 1.0:
+            self.weight = (self.weight * scale).contiguous()
+
+
+register_part("norm", "grouped_rmsnorm", GroupedRMSNorm)
 register_part("norm", "rmsnorm", RMSNorm)
 register_part("norm", "layernorm", LayerNorm)

@@ -32,7 +32,7 @@ class TensorSpec:
     """A tensor a part expects in the checkpoint (src/model_config.cpp:78-97).
 
     ``init`` names the rule of the random-weights mode: "matrix" draws N(0, std),
-    "norm" draws 1 + N(0, std), "zeros" and "ones" are constant.
+    "norm" draws 1 + N(0, std), "uniform" draws from [0, std), "zeros" and "ones" are constant.
     ``optional`` tensors may be absent (a tied output head).
     """
 

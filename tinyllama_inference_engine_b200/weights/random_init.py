@@ -32,6 +32,8 @@ def random_tensors(expected: Iterable[TensorSpec], seed: int, dtype: torch.dtype
             value = torch.randn(spec.shape, generator=generator, dtype=torch.float32) * spec.std
         elif spec.init == "norm":
             value = 1.0 + torch.randn(spec.shape, generator=generator, dtype=torch.float32) * spec.std
+        elif spec.init == "uniform":
+            value = torch.rand(spec.shape, generator=generator, dtype=torch.float32) * spec.std
         elif spec.init == "zeros":
             value = torch.zeros(spec.shape, dtype=torch.float32)
         elif spec.init == "ones":
