@@ -40,12 +40,15 @@ def causal_conv(x, taps, bias=None):
 
 def embed(tokens, P, cfg):
     """Token row times a constant, plus a row of the bigram table chosen by (previous token, token), then the model's norm."""
-    bigram = cfg["embedding"]["bigram"]
-    buckets = int(bigram["buckets"])
+    bigram = cfg["embedding"].get("bigram")
     rows = []
     for t, token in enumerate(tokens):
-        index = buckets if t == 0 else (int(tokens[t - 1]) * int(bigram["mul_prev"]) + int(token) * int(bigram["mul_cur"])) % buckets
-        rows.append(P["embed"][int(token)] * cfg["embedding"]["scale"] + P["bigram"][index])
+        row = P["embed"][int(token)] * cfg["embedding"]["scale"]
+        if bigram is not None:
+            buckets = int(bigram["buckets"])
+            index = buckets if t == 0 else (int(tokens[t - 1]) * int(bigram["mul_prev"]) + int(token) * int(bigram["mul_cur"])) % buckets
+            row = row + P["bigram"][index]
+        rows.append(row)
     x = torch.stack(rows)
     return grouped_rms_norm(x, P["embed.norm"], cfg["norm"]["groups"], cfg["norm"]["eps"])
 
@@ -184,11 +187,13 @@ def layer_forward(x, P, index: int, layer, cfg, angle_dtype=None):
     groups, eps, mult = cfg["norm"]["groups"], cfg["norm"]["eps"], cfg["residual_mult"]
     name = f"l{index}"
     h = grouped_rms_norm(x, P[f"{name}.norm1"], groups, eps)
-    h = h + causal_conv(h, P[f"{name}.canon1"])
+    if cfg.get("canon"):
+        h = h + causal_conv(h, P[f"{name}.canon1"])
     x = x + mult * grouped_rms_norm(mixer(h, P, f"{name}.mix", layer, eps, angle_dtype), P[f"{name}.norm1b"], groups, eps)
     if layer.get("mlp") is not None:
         h = grouped_rms_norm(x, P[f"{name}.norm2"], groups, eps)
-        h = h + causal_conv(h, P[f"{name}.canon2"])
+        if cfg.get("canon"):
+            h = h + causal_conv(h, P[f"{name}.canon2"])
         x = x + mult * grouped_rms_norm(routed_experts(h, P, f"{name}.mlp", layer["mlp"]), P[f"{name}.norm2b"], groups, eps)
     return x
 

@@ -101,15 +101,19 @@ def expected_rows(steps: list[dict], full_logits: dict[str, torch.Tensor]) -> di
     return out
 
 
-def run_and_compare(runner, steps: list[dict], full_logits: dict[str, torch.Tensor], atol: float, rtol: float = 0.0, over_vocabulary: bool = False) -> float:
+def run_and_compare(runner, steps: list[dict], full_logits: dict[str, torch.Tensor], atol: float, rtol: float = 0.0, over_vocabulary: bool = False,
+                    allowed_over: float = 0.0) -> float:
     """Replay the steps through the engine's step function; returns the largest error seen.
 
     ``over_vocabulary``: a row's error is the root mean square of its differences over the vocabulary (what rounding noise that a
-    model amplifies looks like) instead of its largest difference."""
+    model amplifies looks like) instead of its largest difference.  ``allowed_over``: the share of wanted rows that may lie beyond the
+    bound (a model that chooses among experts turns a rounding difference into another choice now and then, and such a row, and in a
+    recurrent model the rows behind it, then differs by far more than rounding); the median row must then lie within a third of the bound."""
     from tinyllama_inference_engine_b200.engine.replay import replay_step
 
     expected = expected_rows(steps, full_logits)
     worst = 0.0
+    row_errors, over = [], []
     for step in steps:
         got = replay_step(runner, step)
         if step["step"] in expected:
@@ -119,7 +123,10 @@ def run_and_compare(runner, steps: list[dict], full_logits: dict[str, torch.Tens
             if over_vocabulary:
                 error = (error * error).mean(dim=1, keepdim=True).sqrt().expand_as(want)
             bound = atol + rtol * want.abs()
-            if not bool((error <= bound).all()):
+            if allowed_over > 0.0:
+                row_errors += (error - rtol * want.abs()).max(dim=1).values.tolist()
+                over += [(step["step"], r) for r in range(want.shape[0]) if not bool((error[r] <= bound[r]).all())]
+            elif not bool((error <= bound).all()):
                 row = int((error - bound).max(1).values.argmax())
                 raise AssertionError(
                     f"step {step['step']}: wanted row {row} differs by {float(error[row].max()):.3e} (bound {atol:.1e}); entries "
@@ -128,4 +135,7 @@ def run_and_compare(runner, steps: list[dict], full_logits: dict[str, torch.Tens
             worst = max(worst, float(error.max()))
         else:
             assert got is None
+    if allowed_over > 0.0 and row_errors:
+        assert len(over) <= allowed_over * len(row_errors), f"{len(over)} of {len(row_errors)} wanted rows beyond {atol:.1e}: (step, row) {over[:8]}"
+        assert float(np.median(row_errors)) <= atol / 3.0, f"the median row differs by {float(np.median(row_errors)):.3e} (a third of the bound is {atol / 3.0:.1e})"
     return worst

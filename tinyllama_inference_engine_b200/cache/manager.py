@@ -253,7 +253,8 @@ class CacheManager:
                 cache.plane_pages = tuple(tensor[position] for tensor in group.plane_tensors)
             if "state" in member:
                 group_index, position = member["state"]
-                cache.state = self.state_groups[group_index].tensor[position]
+                tensor = self.state_groups[group_index].tensor
+                cache.state = None if tensor is None else tensor[position]
             caches[stream] = cache
         return caches
 
