@@ -424,6 +424,37 @@ def redasun_config(size: dict, extra: dict) -> dict:
     return {"architecture": "Redasun", "vocab": size["vocab"], "width": size["width"], "norm": {"eps": 1e-5}, "embedding": {"scale": size["width"] ** 0.5}, "layers": layers}
 
 
+# `--designs kilurax`: Kilurax (softmax attention with biased projections and a partial rotation side by side with a state-space layer; a
+# linear-attention layer whose forget gate also writes; the gated delta rule with one decay per head; grouped RMS norms before and after every
+# sublayer, a short convolution in front of each; a mixture of experts that read their token times its score, beside a shared expert, in every
+# layer; an embedding that also reads the token before) beside Redasun, the closest of the engine's designs (norms before and after every
+# sublayer, attention over pages, a mixture of experts beside a shared one), at equal width, layer count and vocabulary and as wide experts.
+KILURAX_SIZES = {
+    "w2048": dict(left=dict(heads=16, kv_heads=4, dim=128, vdim=128, rot=64), right=dict(heads=32, vdim=64, state=128, groups=1, conv=4, norm_groups=1),
+                  hgrn2=dict(heads=16, dim=128, vdim=128), delta=dict(heads=16, kv_heads=16, dim=128, vdim=128, conv=4), experts=32, top=4, expert_ff=1408, shared_ff=1408,
+                  norm_groups=4, taps=3, pattern=("parallel", "hgrn2", "delta", "hgrn2")),
+    "w4096": dict(left=dict(heads=32, kv_heads=8, dim=128, vdim=128, rot=64), right=dict(heads=64, vdim=64, state=128, groups=1, conv=4, norm_groups=1),
+                  hgrn2=dict(heads=32, dim=128, vdim=128), delta=dict(heads=32, kv_heads=32, dim=128, vdim=128, conv=4), experts=32, top=4, expert_ff=3584, shared_ff=3584,
+                  norm_groups=4, taps=3, pattern=("parallel", "delta", "hgrn2", "parallel")),
+}
+
+
+def kilurax_config(size: dict, extra: dict) -> dict:
+    layers = []
+    for index in range(size["layers"]):
+        kind = extra["pattern"][index % len(extra["pattern"])]
+        if kind == "parallel":
+            left, right = extra["left"], extra["right"]
+            mixer = {"left": {"heads": left["heads"], "kv_heads": left["kv_heads"], "dim": left["dim"], "vdim": left["vdim"], "scale": left["dim"] ** -0.5,
+                              "rot": {"base": 10000.0, "dims": left["rot"]}}, "right": dict(right), "left_scale": 0.7, "right_scale": 0.7}
+        else:
+            mixer = dict(extra[kind])
+        mlp = {"kind": "moe", "expert": {"ff": extra["expert_ff"]}, "shared": {"ff": extra["shared_ff"]}, "router": {"experts": extra["experts"], "top": extra["top"]}}
+        layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Kilurax", "vocab": size["vocab"], "width": size["width"], "norm": {"eps": 1e-5, "groups": extra["norm_groups"]}, "residual_mult": 0.5,
+            "embedding": {"scale": size["width"] ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}}, "canon": {"taps": extra["taps"]}, "layers": layers}
+
+
 def run_designs(args) -> dict:
     import numpy as np
     import torch
@@ -713,13 +744,142 @@ def run_designs(args) -> dict:
                                     "like_ms": like_norm_ms, "like_gbs": norm_moved / like_norm_ms / 1e6, "like_frac": norm_moved / (like_norm_ms / 1e3) / 1e9 / peak["hbm_gbs"]}
         return out
 
+    def kilurax_kernel_numbers(size: dict, extra: dict, like: dict) -> dict:
+        """Kilurax's own kernels alone against their rooflines, beside the like kernels of the closest designs at the same sizes: the recurrence without
+        the correction beside Zirutar's delta rule (the same kernel, one more dot product per row), each mixer's preparation beside the delta rule's, the
+        experts that read their token times its score beside experts whose output is weighed, the grouped norm beside the ungrouped one, and the small
+        per-token kernels (convolution in front of a sublayer, embedding with the token before, biases + rotation + cache write) beside the add + norm."""
+        W, page, bf16 = size["width"], 64, torch.bfloat16
+        E, top, F = extra["experts"], extra["top"], extra["expert_ff"]
+        out = {}
+        gate_up = (torch.randn(E, 2 * F, W, device=device) * W ** -0.5).to(bf16)
+        down = (torch.randn(E, W, F, device=device) * F ** -0.5).to(bf16)
+        router = torch.randn(E, W, device=device) * W ** -0.5
+        left = extra["left"]
+        H, G, D, VD = left["heads"], left["kv_heads"], left["dim"], left["vdim"]
+        pages_needed = -(-(context + 1) // page) * batch + -(-prompt_tokens // page)
+        pages = torch.randn(pages_needed, 2, G, page, D, device=device).to(bf16) if D == VD else None
+        planes = () if D == VD else (torch.randn(pages_needed, G, page, D, device=device).to(bf16), torch.randn(pages_needed, G, page, VD, device=device).to(bf16))
+        inv_freq = torch.tensor([10000.0 ** (-2.0 * i / left["rot"]) for i in range(left["rot"] // 2)], dtype=torch.float32, device=device)
+        biases = tuple(torch.randn(n, device=device) for n in (H * D, G * D, G * VD))
+
+        def context_for(lens, firsts):
+            table_width = size["positions"] // page
+            rows, at = [], 0
+            for n, f in zip(lens, firsts):
+                count = -(-(f + n) // page)
+                rows.append(list(range(at, at + count)) + [-1] * (table_width - count))
+                at += count
+            entries = [StepEntry(i, [0] * n, []) for i, n in enumerate(lens)]
+            return pack_step(entries, list(firsts), list(range(len(lens))), [rows], device)
+
+        recurrences = {"state_space": (extra["right"]["heads"], extra["right"]["groups"], extra["right"]["state"], extra["right"]["vdim"], True),
+                       "hgrn2": (extra["hgrn2"]["heads"], extra["hgrn2"]["heads"], extra["hgrn2"]["dim"], extra["hgrn2"]["vdim"], True),
+                       "delta_per_head": (extra["delta"]["heads"], extra["delta"]["kv_heads"], extra["delta"]["dim"], extra["delta"]["vdim"], False),
+                       "like_delta_per_channel": (like["delta_heads"], like["delta_heads"], like["delta_dim"], like["delta_vdim"], False)}
+        for name, lens, firsts in (("prefill", [prompt_tokens], [0]), ("decode", [1] * batch, [context] * batch)):
+            ctx = context_for(lens, firsts)
+            tokens = sum(lens)
+            for key, (heads, kv, dim, vdim, plain) in recurrences.items():
+                words, _ = ops.delta_state_words(heads, dim, vdim, 0, 1)
+                state = torch.zeros(len(lens), words, device=device)
+                prep = torch.rand(tokens, 2 * kv * dim + heads * (vdim + 1 + dim), device=device) * 0.5
+                read = torch.empty(tokens, heads * vdim, device=device)
+                ms = timed(lambda: ops.delta_rule(prep, state, ctx, read, heads, kv, dim, vdim, plain=plain))
+                moved = prep.numel() * 4.0 + read.numel() * 4.0 + 2.0 * state.numel() * 4.0
+                out[f"recurrence_{key}_{name}"] = {"ms": ms, "gbs": moved / ms / 1e6, "frac": moved / (ms / 1e3) / 1e9 / peak["hbm_gbs"], "heads": heads, "dim": dim, "vdim": vdim}
+            # each mixer's preparation (32-bit rows for the recurrence) and what follows the recurrence
+            r = extra["right"]
+            inner, gn = r["heads"] * r["vdim"], r["groups"] * r["state"]
+            rows = torch.randn(tokens, 2 * inner + 2 * gn + r["heads"], device=device).to(bf16)
+            words, conv_at = ops.delta_state_words(r["heads"], r["state"], r["vdim"], inner + 2 * gn, r["conv"])
+            state = torch.zeros(len(lens), words, device=device)
+            prep = torch.empty(tokens, 2 * gn + inner + r["heads"] + r["heads"] * r["state"], device=device)
+            taps, conv_bias = torch.randn(inner + 2 * gn, r["conv"], device=device), torch.randn(inner + 2 * gn, device=device)
+            per_head = torch.randn(r["heads"], device=device)
+            ms = timed(lambda: ops.ssd_prepare(rows, taps, conv_bias, per_head, per_head, state, conv_at, ctx, prep, r["heads"], r["groups"], r["state"], r["vdim"]))
+            moved = rows.numel() * 2.0 + prep.numel() * 4.0
+            out[f"prepare_state_space_{name}"] = {"ms": ms, "gbs": moved / ms / 1e6, "frac": moved / (ms / 1e3) / 1e9 / peak["hbm_gbs"]}
+            read, gated = torch.randn(tokens, inner, device=device), torch.empty(tokens, inner, dtype=bf16, device=device)
+            ms = timed(lambda: ops.ssd_finish(read, prep, 2 * gn, rows, per_head, torch.ones(inner, device=device), gated, 1e-5, r["heads"], r["vdim"], r["norm_groups"]))
+            moved = inner * tokens * (4.0 + 4.0 + 2.0 + 2.0)
+            out[f"finish_state_space_{name}"] = {"ms": ms, "gbs": moved / ms / 1e6, "frac": moved / (ms / 1e3) / 1e9 / peak["hbm_gbs"]}
+            h = extra["hgrn2"]
+            rows = torch.randn(tokens, 2 * h["heads"] * h["dim"] + h["heads"] * h["vdim"], device=device).to(bf16)
+            prep = torch.empty(tokens, 3 * h["heads"] * h["dim"] + h["heads"] * h["vdim"] + h["heads"], device=device)
+            lower = torch.rand(h["heads"] * h["dim"], device=device)
+            ms = timed(lambda: ops.hgrn2_prepare(rows, lower, lower, prep, h["heads"], h["dim"], h["vdim"]))
+            moved = rows.numel() * 2.0 + prep.numel() * 4.0
+            out[f"prepare_hgrn2_{name}"] = {"ms": ms, "gbs": moved / ms / 1e6, "frac": moved / (ms / 1e3) / 1e9 / peak["hbm_gbs"]}
+            for key, (heads, kv, dim, vdim, per) in {"delta_per_head": (extra["delta"]["heads"], extra["delta"]["kv_heads"], extra["delta"]["dim"], extra["delta"]["vdim"], True),
+                                                     "like_delta_per_channel": (like["delta_heads"], like["delta_heads"], like["delta_dim"], like["delta_vdim"], False)}.items():
+                channels = 2 * kv * dim + heads * vdim
+                rows = torch.randn(tokens, channels + 2 * heads, device=device).to(bf16)
+                decay_in = rows[:, channels + heads :] if per else torch.randn(tokens, heads * dim, device=device).to(bf16)
+                words, conv_at = ops.delta_state_words(heads, dim, vdim, channels, 4)
+                state = torch.zeros(len(lens), words, device=device)
+                prep = torch.empty(tokens, channels + heads + heads * dim, device=device)
+                taps = torch.randn(channels, 4, device=device)
+                a_log, dt_bias = torch.randn(heads, device=device), torch.randn(heads if per else heads * dim, device=device)
+                ms = timed(lambda: ops.delta_prepare(rows, channels, decay_in, taps, a_log, dt_bias, state, conv_at, ctx, prep, heads, kv, dim, vdim, 1e-6, dim ** -0.5, decay_per_head=per))
+                moved = rows.numel() * 2.0 + prep.numel() * 4.0 + (0 if per else decay_in.numel() * 2.0)
+                out[f"prepare_{key}_{name}"] = {"ms": ms, "gbs": moved / ms / 1e6, "frac": moved / (ms / 1e3) / 1e9 / peak["hbm_gbs"]}
+            # experts: the score on what the expert reads, beside the weight on what it returns
+            x = torch.randn(tokens, W, device=device).to(bf16)
+            ids = torch.empty(tokens, top, dtype=torch.int32, device=device)
+            weights = torch.empty(tokens, top, device=device)
+            route_ms = timed(lambda: ops.moe_route(x, router, None, ids, weights, 1, 1, 1.0, normalize=False))
+            routed = torch.empty(tokens, W, dtype=bf16, device=device)
+            experts_ms = timed(lambda: ops.moe_experts(x, gate_up, down, ids, weights, None, routed, "silu", batch=ctx, weight_input=True))
+            like_ms = timed(lambda: ops.moe_experts(x, gate_up, down, ids, weights, None, routed, "silu", batch=ctx))
+            if name == "prefill":
+                ff_flops = tokens * top * 3 * 2.0 * F * W
+                out["experts_prefill"] = {"ms": experts_ms, "route_ms": route_ms, "tflops": ff_flops / experts_ms / 1e9, "frac": ff_flops / (experts_ms / 1e3) / (peak["bf16_tflops"] * 1e12),
+                                          "like_ms": like_ms, "like_frac": ff_flops / (like_ms / 1e3) / (peak["bf16_tflops"] * 1e12)}
+            else:
+                ff_moved = len(torch.unique(ids)) * 3.0 * F * W * 2.0
+                out["experts_decode"] = {"ms": experts_ms, "route_ms": route_ms, "gbs": ff_moved / experts_ms / 1e6, "frac": ff_moved / (experts_ms / 1e3) / 1e9 / peak["hbm_gbs"],
+                                         "like_ms": like_ms, "like_frac": ff_moved / (like_ms / 1e3) / 1e9 / peak["hbm_gbs"]}
+            # row-wise kernels: the grouped norm around a branch, the convolution in front of a sublayer, the embedding, the cache write
+            stream, y = torch.zeros(tokens, W, device=device), torch.randn(tokens, W, device=device).to(bf16)
+            normed, ones = torch.empty(tokens, W, dtype=bf16, device=device), torch.ones(W, device=device)
+            norm_ms = timed(lambda: ops.branch_norm(stream, y, ones, ones, normed, 1e-5, False, groups=extra["norm_groups"]))
+            like_norm_ms = timed(lambda: ops.branch_norm(stream, y, ones, ones, normed, 1e-5, True))
+            norm_moved = tokens * W * (2 + 4 + 4 + 2.0)
+            out[f"norms_{name}"] = {"ms": norm_ms, "gbs": norm_moved / norm_ms / 1e6, "frac": norm_moved / (norm_ms / 1e3) / 1e9 / peak["hbm_gbs"],
+                                    "like_ms": like_norm_ms, "like_frac": norm_moved / (like_norm_ms / 1e3) / 1e9 / peak["hbm_gbs"]}
+            kept = torch.zeros(len(lens), (extra["taps"] - 1) * W, device=device)
+            conv_taps, filtered = torch.randn(W, extra["taps"], device=device), torch.empty(tokens, W, dtype=bf16, device=device)
+            conv_ms = timed(lambda: ops.conv_residual(y, conv_taps, kept, 0, ctx, filtered))
+            out[f"input_convolution_{name}"] = {"ms": conv_ms, "gbs": tokens * W * 4.0 / conv_ms / 1e6, "frac": tokens * W * 4.0 / (conv_ms / 1e3) / 1e9 / peak["hbm_gbs"]}
+            table, pairs = torch.randn(size["vocab"], W, device=device).to(bf16), torch.randn(65522, W, device=device).to(bf16)
+            word = torch.zeros(len(lens), 1, device=device)
+            embed_ms = timed(lambda: ops.pair_embedding(table, pairs, ctx, word, 0, ones, 1e-5, 3.0, stream, 65521, 31, 7, extra["norm_groups"]))
+            out[f"pair_embedding_{name}"] = {"ms": embed_ms, "gbs": tokens * W * 8.0 / embed_ms / 1e6, "frac": tokens * W * 8.0 / (embed_ms / 1e3) / 1e9 / peak["hbm_gbs"]}
+            cache = LayerCache(CacheNeed("pages"), True, pages, ctx.block_tables[0], page, None, planes)
+            qkv = torch.randn(tokens, (H + G) * D + G * VD, device=device).to(bf16)
+            store_ms = timed(lambda: ops.rotary_store_planes(qkv, H * D, (H + G) * D, biases, inv_freq, left["rot"], ctx.positions, ctx.token_seq, cache, H, G, D, VD))
+            like_store_ms = timed(lambda: ops.store_kv_planes(qkv, H * D, (H + G) * D, ctx.positions, ctx.token_seq, cache, G, D, VD))
+            mixed = torch.empty(tokens, H * VD, dtype=bf16, device=device)
+            ms = timed(lambda: ops.mixed_heads_attention(qkv, -1, ctx.positions, ctx.token_seq, cache, None, None, mixed, H, G, D, VD, 0, D ** -0.5, batch=ctx))
+            causal = sum(f + i + 1 for n, f in zip(lens, firsts) for i in range(n))
+            if name == "prefill":
+                flops = causal * H * 2.0 * (D + VD)
+                out["attention_prefill"] = {"ms": ms, "tflops": flops / ms / 1e9, "frac": flops / (ms / 1e3) / (peak["bf16_tflops"] * 1e12), "store_ms": store_ms, "like_store_ms": like_store_ms}
+            else:
+                moved = causal * G * (D + VD) * 2.0
+                out["attention_decode"] = {"ms": ms, "gbs": moved / ms / 1e6, "frac": moved / (ms / 1e3) / 1e9 / peak["hbm_gbs"], "store_ms": store_ms, "like_store_ms": like_store_ms}
+        return out
+
     results = {}
     which = args.designs
     with ClockSampler() as clocks:
         for key, size in DESIGN_SIZES.items():
             marutar, llama = design_configs(size)
             base = Path(tempfile.gettempdir()) / f"tlie_b200_designs_{os.getuid()}_{key}"
-            if which == "redasun":
+            if which == "kilurax":
+                pair = (("kilurax", kilurax_config(size, KILURAX_SIZES[key])), ("redasun", redasun_config(size, REDASUN_SIZES[key])))
+            elif which == "redasun":
                 pair = (("redasun", redasun_config(size, REDASUN_SIZES[key])), ("llama", llama))
             else:
                 pair = (("marutar", marutar), ("llama", llama)) if which == "marutar" else (("zirutar", zirutar_config(size, ZIRUTAR_SIZES[key])), ("marutar", marutar))
@@ -729,16 +889,21 @@ def run_designs(args) -> dict:
                 if not (folders[name] / "model.safetensors").exists():
                     write_random_model(folders[name], config, seed=0)
             results[key] = {name: model_numbers(folders[name]) for name, _ in pair}
-            if which == "redasun":
+            if which == "kilurax":
+                results[key]["kernels"] = kilurax_kernel_numbers(size, KILURAX_SIZES[key], ZIRUTAR_SIZES[key])
+            elif which == "redasun":
                 results[key]["kernels"] = redasun_kernel_numbers(size, REDASUN_SIZES[key])
             else:
                 results[key]["kernels"] = kernel_numbers(size) if which == "marutar" else zirutar_kernel_numbers(size, ZIRUTAR_SIZES[key])
             results[key]["sizes"] = {k: v for k, v in size.items() if k != "pattern"} | {"pattern": "/".join(size["pattern"])}
             if which == "redasun":
                 results[key]["sizes"] = {k: v for k, v in size.items() if k in ("width", "ff", "vocab", "layers")} | {k: (list(v) if isinstance(v, tuple) else v) for k, v in REDASUN_SIZES[key].items()}
+            if which == "kilurax":
+                results[key]["sizes"] = {k: v for k, v in size.items() if k in ("width", "vocab", "layers")} | {k: (list(v) if isinstance(v, tuple) else v) for k, v in KILURAX_SIZES[key].items()}
             if which == "zirutar":
                 results[key]["sizes"] |= {k: v for k, v in ZIRUTAR_SIZES[key].items() if k != "pattern"} | {"zirutar_pattern": "/".join(ZIRUTAR_SIZES[key]["pattern"])}
-    names = {"marutar": "Marutar beside the Llama decoder", "zirutar": "Zirutar beside Marutar", "redasun": "Redasun beside the Llama decoder"}[which]
+    names = {"marutar": "Marutar beside the Llama decoder", "zirutar": "Zirutar beside Marutar", "redasun": "Redasun beside the Llama decoder",
+             "kilurax": "Kilurax beside Redasun"}[which]
     return {"metric": f"prompt and decode throughput of {names} at equal sizes", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
             "data": "synthetic (random weights, uniform random token ids)", "impl": "engine", "higher_is_better": True,
             "config": {"prompt_tokens": prompt_tokens, "decode_context": context, "decode_batch": batch, "decode_steps": steps, "page_size": 64, "peaks": peak_kind,
@@ -799,9 +964,9 @@ def main() -> int:
     parser.add_argument("--impl", default="engine", choices=["engine", "reference"])
     parser.add_argument("--reference-points", action="store_true", help="with --impl reference: also time batch 1 and 64 (minutes)")
     parser.add_argument("--sections", default="decode,e2e,prefill,points,mixed", help="which measurements to take (fewer for profiling runs; `mixed` adds requests of mixed length through the scheduler)")
-    parser.add_argument("--designs", nargs="?", const="marutar", default=None, choices=["marutar", "zirutar", "redasun"],
+    parser.add_argument("--designs", nargs="?", const="marutar", default=None, choices=["marutar", "zirutar", "redasun", "kilurax"],
                         help="instead of the headline workload: another design beside the closest existing one at equal sizes (prompt and decode throughput through "
-                             "the engine, and the design's own kernels against their rooflines): Marutar beside the Llama decoder (the default), or Zirutar beside Marutar")
+                             "the engine, and the design's own kernels against their rooflines): Marutar beside the Llama decoder (the default), Zirutar beside Marutar, Redasun beside the Llama decoder, or Kilurax beside Redasun")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU only: this engine is single-GPU by design (asked for {args.gpus})")

@@ -52,18 +52,29 @@ __global__ void store_kv_planes_kernel(const T* __restrict__ rows, int row_strid
 // Each vector gets its bias (32-bit, null: none); of every q and k head the first ``rot_dims`` columns turn, column i with column
 // i + rot_dims / 2, by position * inv_freq[i] (angle, sine and cosine in 32-bit); q is left in place, k and v go into the token's page.
 template <typename T>
-__global__ void __launch_bounds__(128) rotary_store_planes_kernel(T* __restrict__ rows, int row_stride, int k_offset, int v_offset, const float* __restrict__ q_bias,
+__global__ void __launch_bounds__(256) rotary_store_planes_kernel(T* __restrict__ rows, int row_stride, int k_offset, int v_offset, const float* __restrict__ q_bias,
                                                                   const float* __restrict__ k_bias, const float* __restrict__ v_bias, const float* __restrict__ inv_freq,
                                                                   int rot_dims, const int* __restrict__ positions, const int* __restrict__ token_seq,
                                                                   const int* __restrict__ block_table, int table_stride, T* __restrict__ k_pages, long long k_page_stride,
                                                                   T* __restrict__ v_pages, long long v_page_stride, int heads, int kv_heads, int key_dim, int value_dim,
                                                                   int page_size, int write_cache) {
+  extern __shared__ float turn_s[];   // the token's cosines [rot_dims / 2], then its sines: worked out once, used by every head
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int page = write_cache ? block_table[(size_t)token_seq[t] * table_stride + pos / page_size] : -1;
   const int slot = pos % page_size;
   T* row = rows + (size_t)t * row_stride;
   const int half = rot_dims / 2;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &turn_s[half + i], &turn_s[i]);
+  // values first: they need no angle
+  if (page >= 0)
+    for (int i = threadIdx.x; i < kv_heads * value_dim; i += blockDim.x) {
+      const int head = i / value_dim, d = i - head * value_dim;
+      float a = to_float(row[v_offset + i]);
+      if (v_bias != nullptr) a += v_bias[i];
+      v_pages[(size_t)page * v_page_stride + ((size_t)head * page_size + slot) * value_dim + d] = from_float<T>(a);
+    }
+  __syncthreads();
   const int units = key_dim - half;   // per head: ``half`` pairs, then the columns that do not turn
   for (int i = threadIdx.x; i < (heads + kv_heads) * units; i += blockDim.x) {
     const int h = i / units, u = i - h * units;
@@ -75,8 +86,7 @@ __global__ void __launch_bounds__(128) rotary_store_planes_kernel(T* __restrict_
     if (u < half) {
       float a = to_float(vec[u]), b = to_float(vec[u + half]);
       if (bias != nullptr) a += bias[head * key_dim + u], b += bias[head * key_dim + u + half];
-      float sine, cosine;
-      sincosf((float)pos * inv_freq[u], &sine, &cosine);
+      const float cosine = turn_s[u], sine = turn_s[half + u];
       const T first = from_float<T>(a * cosine - b * sine), second = from_float<T>(b * cosine + a * sine);
       if (!is_key) vec[u] = first, vec[u + half] = second;
       if (dst != nullptr) dst[u] = first, dst[u + half] = second;
@@ -88,13 +98,6 @@ __global__ void __launch_bounds__(128) rotary_store_planes_kernel(T* __restrict_
       if (!is_key) vec[d] = value;
       if (dst != nullptr) dst[d] = value;
     }
-  }
-  if (page < 0) return;
-  for (int i = threadIdx.x; i < kv_heads * value_dim; i += blockDim.x) {
-    const int head = i / value_dim, d = i - head * value_dim;
-    float a = to_float(row[v_offset + i]);
-    if (v_bias != nullptr) a += v_bias[i];
-    v_pages[(size_t)page * v_page_stride + ((size_t)head * page_size + slot) * value_dim + d] = from_float<T>(a);
   }
 }
 
@@ -587,13 +590,13 @@ TLIE_EXPORT int tlie_rotary_store_planes(int dtype, void* rows, int row_stride, 
                                          void* k_pages, long long k_page_stride, void* v_pages, long long v_page_stride, int tokens, int heads, int kv_heads, int key_dim,
                                          int value_dim, int page_size, int write_cache, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (rot_dims < 0 || rot_dims % 2 || rot_dims > key_dim || (rot_dims > 0 && inv_freq == nullptr)) return (int)cudaErrorInvalidValue;
+  if (rot_dims < 0 || rot_dims % 2 || rot_dims > key_dim || rot_dims > 8192 || (rot_dims > 0 && inv_freq == nullptr)) return (int)cudaErrorInvalidValue;
   if (dtype == TLIE_F32)
-    rotary_store_planes_kernel<float><<<tokens, 128, 0, stream>>>((float*)rows, row_stride, k_offset, v_offset, q_bias, k_bias, v_bias, inv_freq, rot_dims, positions,
+    rotary_store_planes_kernel<float><<<tokens, 256, (size_t)rot_dims * sizeof(float), stream>>>((float*)rows, row_stride, k_offset, v_offset, q_bias, k_bias, v_bias, inv_freq, rot_dims, positions,
                                                                   token_seq, block_table, table_stride, (float*)k_pages, k_page_stride, (float*)v_pages, v_page_stride,
                                                                   heads, kv_heads, key_dim, value_dim, page_size, write_cache);
   else
-    rotary_store_planes_kernel<__nv_bfloat16><<<tokens, 128, 0, stream>>>((__nv_bfloat16*)rows, row_stride, k_offset, v_offset, q_bias, k_bias, v_bias, inv_freq, rot_dims,
+    rotary_store_planes_kernel<__nv_bfloat16><<<tokens, 256, (size_t)rot_dims * sizeof(float), stream>>>((__nv_bfloat16*)rows, row_stride, k_offset, v_offset, q_bias, k_bias, v_bias, inv_freq, rot_dims,
                                                                           positions, token_seq, block_table, table_stride, (__nv_bfloat16*)k_pages, k_page_stride,
                                                                           (__nv_bfloat16*)v_pages, v_page_stride, heads, kv_heads, key_dim, value_dim, page_size,
                                                                           write_cache);

@@ -7,6 +7,8 @@
 //                (expert, first row, rows); nothing is read back on the host, the grids are sized for the most tiles there can be.
 //   moe_grouped  <GATED>  act[p] = act(W_gate[e] x[token(p)]) * (W_up[e] x[token(p)])       for the sorted rows p of expert e
 //                <DOWN>   y[slot(p)] = weight[slot(p)] * W_down[e] act[p]                    32-bit, by slot
+//                ``weight_input``: the weight multiplies what the expert reads instead (its two first products are linear in it, so
+//                act(w g) * (w u) in the gated epilogue, 32-bit, and no weight behind W_down)
 //                64 x 64 tiles (the gated one: 64 gate and the 64 up columns beside them), k in blocks of 32 through two cp.async
 //                stages, mma.sync m16n8k16 with 32-bit accumulators, a warp per 16 rows.
 //   moe_combine  out[t] = sum_k y[t * top + k] + shared[t]: the chosen experts in the order they were chosen, so that a row's
@@ -57,7 +59,7 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
 template <bool GATED>
 __global__ void __launch_bounds__(kGThreads) moe_grouped_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, const int* __restrict__ sorted_slots,
                                                                 const int* __restrict__ meta, const float* __restrict__ weights, void* __restrict__ out, int N, int K,
-                                                                int top, int kind) {
+                                                                int top, int kind, int weight_input) {
   constexpr int kB = GATED ? 2 : 1;
   __shared__ __align__(16) __nv_bfloat16 a_s[2][kGM][kGRow];
   __shared__ __align__(16) __nv_bfloat16 b_s[2][kB][kGN][kGRow];
@@ -124,16 +126,17 @@ __global__ void __launch_bounds__(kGThreads) moe_grouped_kernel(const __nv_bfloa
     if (row >= rows) continue;
     if (GATED) {
       __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)(row0 + row) * N;
+      const float scale = weight_input ? weights[row_slot[row]] : 1.0f;
 #pragma unroll
       for (int j = 0; j < kGN / 8; ++j)
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           const int n = n0 + j * 8 + 2 * t + c;
-          if (n < N) dst[n] = __float2bfloat16_rn(grouped_act(acc[0][j][r * 2 + c], kind) * acc[kB - 1][j][r * 2 + c]);
+          if (n < N) dst[n] = __float2bfloat16_rn(grouped_act(scale * acc[0][j][r * 2 + c], kind) * (scale * acc[kB - 1][j][r * 2 + c]));
         }
     } else {
       const int slot = row_slot[row];
-      const float weight = weights[slot];
+      const float weight = weight_input ? 1.0f : weights[slot];
       float* dst = reinterpret_cast<float*>(out) + (size_t)slot * N;
 #pragma unroll
       for (int j = 0; j < kGN / 8; ++j)
@@ -164,7 +167,8 @@ using namespace tlie;
 // Scratch: sorted_slots int32 [tokens * top], meta int32 [1 + 3 * (tokens * top / 64 + experts)], act bfloat16 [tokens * top, ff],
 // y 32-bit [tokens * top, width].  ``shared`` bfloat16 [tokens, width] or null.
 TLIE_EXPORT int tlie_moe_grouped(const void* x, const void* gate_up, const void* down, const int* ids, const float* weights, const void* shared, int* sorted_slots,
-                                 int* meta, void* act, float* y, void* out, int tokens, int width, int ff, int experts, int top, int kind, cudaStream_t stream) {
+                                 int* meta, void* act, float* y, void* out, int tokens, int width, int ff, int experts, int top, int kind, int weight_input,
+                                 cudaStream_t stream) {
   if (tokens <= 0) return 0;
   const long long slots = (long long)tokens * top;
   if (width % 8 != 0 || ff % 8 != 0 || experts <= 0 || experts > 4096 || slots > (1LL << 30) || kind < 0 || kind > 1) return (int)cudaErrorInvalidValue;
@@ -173,11 +177,11 @@ TLIE_EXPORT int tlie_moe_grouped(const void* x, const void* gate_up, const void*
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   moe_grouped_kernel<true><<<dim3(max_tiles, (ff + kGN - 1) / kGN), kGThreads, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)gate_up, sorted_slots, meta,
-                                                                                            weights, act, ff, width, top, kind);
+                                                                                            weights, act, ff, width, top, kind, weight_input);
   e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   moe_grouped_kernel<false><<<dim3(max_tiles, (width + kGN - 1) / kGN), kGThreads, 0, stream>>>((const __nv_bfloat16*)act, (const __nv_bfloat16*)down, sorted_slots, meta,
-                                                                                                weights, y, width, ff, top, kind);
+                                                                                                weights, y, width, ff, top, kind, weight_input);
   e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   const size_t total = (size_t)tokens * width;

@@ -7,7 +7,8 @@
 //   moe_layout     one CTA: counts per expert, their padded running sum, every slot's row, every row's token (-1: padding),
 //                  and the expert of every 128-row tile.  Nothing is read back on the host: grids and scratch are sized for the
 //                  most tiles there can be (slots / 128 + experts) and the kernels read the tile count on the device.
-//   moe_gather     xs[row] = x[token(row)] (zeros for padding rows), so that TMA fetches an expert's rows as one box.
+//   moe_gather     xs[row] = x[token(row)] (zeros for padding rows), so that TMA fetches an expert's rows as one box.  Where the weight
+//                  multiplies what an expert reads (``weight_input``), the row is gathered times its weight and the sum below takes no weights.
 //   moe_tc <GATED> act[row] = act(W_gate[e] xs[row]) * (W_up[e] xs[row])      tile 128 x (128 gate + 128 up columns)
 //          <DOWN>  y[row]   = W_down[e] act[row]                               32-bit, tile 128 x 256
 //   moe_tc_combine out[t] = sum_k weight[t, k] y[row(t, k)] + shared[t]: the chosen experts in the order they were chosen, so
@@ -36,7 +37,7 @@ __device__ __forceinline__ float tc_act(float z) {
   return z / (1.0f + expf(-z));
 }
 
-// meta: [0] number of 128-row tiles, [1 + i] the expert of tile i.  row_of_slot [slots]; token_of_row [max_rows].
+// meta: [0] number of 128-row tiles, [1 + i] the expert of tile i.  row_of_slot [slots]; token_of_row [max_rows] holds the row's slot (token * top + k).
 __global__ void __launch_bounds__(1024) moe_layout_kernel(const int* __restrict__ ids, int slots, int experts, int top, int max_rows, int* __restrict__ row_of_slot,
                                                           int* __restrict__ token_of_row, int* __restrict__ meta) {
   extern __shared__ int layout_smem[];   // counts [experts], cursor [experts]
@@ -60,19 +61,34 @@ __global__ void __launch_bounds__(1024) moe_layout_kernel(const int* __restrict_
   for (int s = threadIdx.x; s < slots; s += blockDim.x) {
     const int row = atomicAdd(&cursor[ids[s]], 1);
     row_of_slot[s] = row;
-    token_of_row[row] = s / top;
+    token_of_row[row] = s;
   }
 }
 
 // a warp per row, 16 bytes a lane at a time
 __global__ void __launch_bounds__(256) moe_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ token_of_row, const int* __restrict__ meta,
-                                                         __nv_bfloat16* __restrict__ xs, int width) {
+                                                         const float* __restrict__ input_weights, __nv_bfloat16* __restrict__ xs, int width, int top) {
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (row >= meta[0] * kBM) return;
-  const int token = token_of_row[row];
+  const int slot = token_of_row[row];
+  const int token = slot < 0 ? -1 : slot / top;
   const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(token < 0 ? 0 : token) * width);
   uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)row * width);
-  for (int i = lane; i < width / 8; i += 32) dst[i] = token < 0 ? make_uint4(0, 0, 0, 0) : src[i];
+  if (input_weights == nullptr || token < 0) {
+    for (int i = lane; i < width / 8; i += 32) dst[i] = token < 0 ? make_uint4(0, 0, 0, 0) : src[i];
+    return;
+  }
+  const float w = input_weights[slot];   // the expert reads its token times the token's weight
+  for (int i = lane; i < width / 8; i += 32) {
+    uint4 raw = src[i];
+    __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(pairs[j]);
+      pairs[j] = __floats2bfloat162_rn(f.x * w, f.y * w);
+    }
+    dst[i] = raw;
+  }
 }
 
 // One warp's 32 rows of a gated tile: act(gate) * up of 32 columns at a time as bfloat16 into a staging box, written by a bulk
@@ -269,7 +285,7 @@ __global__ void __launch_bounds__(256) moe_tc_combine_kernel(const float* __rest
     const int n = (int)(i - t * (width / 4)) * 4;
     float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     for (int k = 0; k < top; ++k) {
-      const float w = weights[t * top + k];
+      const float w = weights != nullptr ? weights[t * top + k] : 1.0f;
       const float4 v = *reinterpret_cast<const float4*>(y + (size_t)row_of_slot[t * top + k] * width + n);
       sum.x = fmaf(w, v.x, sum.x);
       sum.y = fmaf(w, v.y, sum.y);
@@ -318,7 +334,7 @@ using namespace tlie;
 // ``shared`` bfloat16 [tokens, width] or null.  All of 16-byte aligned bases; width and ff multiples of 8.
 TLIE_EXPORT int tlie_moe_grouped_tc(const void* x, const void* gate_up, const void* down, const int* ids, const float* weights, const void* shared, int* row_of_slot,
                                     int* token_of_row, int* meta, void* xs, void* act, float* y, void* out, int tokens, int width, int ff, int experts, int top,
-                                    int kind, int* error_flag, cudaStream_t stream) {
+                                    int kind, int weight_input, int* error_flag, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   const long long slots = (long long)tokens * top;
   if (width % 8 != 0 || ff % 8 != 0 || experts <= 0 || experts > 4096 || slots > (1LL << 30) || kind < 0 || kind > 1 || error_flag == nullptr) return (int)cudaErrorInvalidValue;
@@ -327,7 +343,7 @@ TLIE_EXPORT int tlie_moe_grouped_tc(const void* x, const void* gate_up, const vo
   moe_layout_kernel<<<1, 1024, 2 * experts * sizeof(int), stream>>>(ids, (int)slots, experts, top, max_rows, row_of_slot, token_of_row, meta);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
-  moe_gather_kernel<<<max_rows / 8, 256, 0, stream>>>((const __nv_bfloat16*)x, token_of_row, meta, (__nv_bfloat16*)xs, width);
+  moe_gather_kernel<<<max_rows / 8, 256, 0, stream>>>((const __nv_bfloat16*)x, token_of_row, meta, weight_input ? weights : nullptr, (__nv_bfloat16*)xs, width, top);
   e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   int rc = kind == 1 ? launch_moe_tc<true, 1>(xs, gate_up, act, meta, max_rows, experts * 2 * ff, ff, width, error_flag, stream)
@@ -338,6 +354,6 @@ TLIE_EXPORT int tlie_moe_grouped_tc(const void* x, const void* gate_up, const vo
   const size_t quads = (size_t)tokens * (width / 4);
   const size_t blocks = (quads + 255) / 256;
   const size_t most = (size_t)device_sm_count() * 16;
-  moe_tc_combine_kernel<<<(int)(blocks < most ? blocks : most), 256, 0, stream>>>(y, row_of_slot, weights, (const __nv_bfloat16*)shared, (__nv_bfloat16*)out, width, top, quads);
+  moe_tc_combine_kernel<<<(int)(blocks < most ? blocks : most), 256, 0, stream>>>(y, row_of_slot, weight_input ? nullptr : weights, (const __nv_bfloat16*)shared, (__nv_bfloat16*)out, width, top, quads);
   return (int)cudaGetLastError();
 }

@@ -996,8 +996,8 @@ def moe_experts(x, gate_up, down, ids, weights, shared, out, activation: str = "
         raise KernelError("moe_experts: the shared branch has the output's shape and dtype", code="invalid_shape")
     if activation not in GATE_KINDS:
         raise KernelError(f"moe_experts: no activation {activation!r}", code="invalid_argument")
-    if x.dtype == torch.bfloat16 and not weight_input and fast.moe_grouped_takes(tokens, top, width, ff, experts):
-        fast.moe_grouped(x, gate_up, down, ids, weights, shared, out, GATE_KINDS[activation])
+    if x.dtype == torch.bfloat16 and fast.moe_grouped_takes(tokens, top, width, ff, experts):
+        fast.moe_grouped(x, gate_up, down, ids, weights, shared, out, GATE_KINDS[activation], weight_input)
         return
     act = fast.mixed_scratch(x.device, tokens * top * ff, x.dtype)
     _check(moe_library().tlie_moe_experts(_code(x), _ptr(x), _ptr(gate_up), _ptr(down), _ptr(ids), _ptr(weights), _ptr(shared), _ptr(act), _ptr(out), c_int(tokens),

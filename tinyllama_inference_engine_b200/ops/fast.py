@@ -953,7 +953,7 @@ def moe_grouped_takes(tokens: int, top: int, width: int, ff: int, experts: int) 
     return use_moe_grouped and tokens >= MOE_GROUPED_MIN_ROWS and tokens * top >= MOE_GROUPED_MIN_SLOTS and width % 8 == 0 and ff % 8 == 0 and experts <= 4096
 
 
-def moe_grouped(x, gate_up, down, ids, weights, shared, out, kind: int) -> None:
+def moe_grouped(x, gate_up, down, ids, weights, shared, out, kind: int, weight_input: bool = False) -> None:
     ops = _ops()
     tokens, width = x.shape
     experts, two_ff, _ = gate_up.shape
@@ -971,7 +971,7 @@ def moe_grouped(x, gate_up, down, ids, weights, shared, out, kind: int) -> None:
         y = named_scratch(device, "moe_by_row", max_rows * width, torch.float32)
         ops._check(ops.moe_library().tlie_moe_grouped_tc(ops._ptr(x), ops._ptr(gate_up), ops._ptr(down), ops._ptr(ids), ops._ptr(weights), ops._ptr(shared), ops._ptr(row_of_slot),
                                                          ops._ptr(token_of_row), ops._ptr(meta), ops._ptr(xs), ops._ptr(act), ops._ptr(y), ops._ptr(out), c_int(tokens), c_int(width),
-                                                         c_int(ff), c_int(experts), c_int(top), c_int(kind), ops._ptr(tcgen05_error_flag(device)), ops._stream()), "moe_grouped_tc")
+                                                         c_int(ff), c_int(experts), c_int(top), c_int(kind), c_int(1 if weight_input else 0), ops._ptr(tcgen05_error_flag(device)), ops._stream()), "moe_grouped_tc")
         ops.launch_count += 4   # five kernels: the layout, the gathered rows, two products over all experts, the sum
         return
     sorted_slots = named_scratch(device, "moe_sorted", slots, torch.int32)
@@ -980,5 +980,5 @@ def moe_grouped(x, gate_up, down, ids, weights, shared, out, kind: int) -> None:
     y = named_scratch(device, "moe_by_slot", slots * width, torch.float32)
     ops._check(ops.moe_library().tlie_moe_grouped(ops._ptr(x), ops._ptr(gate_up), ops._ptr(down), ops._ptr(ids), ops._ptr(weights), ops._ptr(shared), ops._ptr(sorted_slots),
                                                   ops._ptr(meta), ops._ptr(act), ops._ptr(y), ops._ptr(out), c_int(tokens), c_int(width), c_int(ff), c_int(experts), c_int(top),
-                                                  c_int(kind), ops._stream()), "moe_grouped")
+                                                  c_int(kind), c_int(1 if weight_input else 0), ops._stream()), "moe_grouped")
     ops.launch_count += 3   # four kernels: the sort, two products per expert, the sum
