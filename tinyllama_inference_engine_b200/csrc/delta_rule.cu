@@ -35,7 +35,7 @@ namespace tlie {
 constexpr int kDeltaLanes = TLIE_DELTA_LANES;        // lanes that share a column of the state (8 or 16; the host lays the state out for the same number)
 constexpr int kDeltaColumns = 128 / kDeltaLanes;     // columns per CTA
 constexpr int kDeltaThreads = kDeltaLanes * kDeltaColumns;
-constexpr int kDeltaMaxTaps = 8;
+constexpr int kDeltaMaxTaps = 16;
 
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + expf(-v)); }
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
@@ -127,10 +127,12 @@ __device__ __forceinline__ void delta_wait() { asm volatile("cp.async.wait_group
 // R: key channels a lane has registers for (a multiple of 4, dim <= 8 R); the state holds 4 ceil(dim / 32) of them per lane.
 // A row's operands ([q | k | g] of the head, the CTA's 16 values, beta) are copied asynchronously into a ring of kDeltaStages
 // buffers, several rows ahead, so that a row's turn never waits for memory; padding words are zeroed once and never copied.
-template <int R>
+// PLAIN: u = beta v needs nothing of the state, so the chain from one row to the next is S <- g S + k u alone and the read-out's sums and
+// shuffles (o = S^T q of the new state) hang off it; with the correction u waits for k . S_j, reduced over the column's lanes, in every row.
+template <int R, bool PLAIN>
 __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* __restrict__ prep, float* __restrict__ state, long long state_stride,
                                                                   const int* __restrict__ seq_starts, const int* __restrict__ state_slots, float* __restrict__ out,
-                                                                  int heads, int kv_heads, int dim, int vdim, float correct) {
+                                                                  int heads, int kv_heads, int dim, int vdim) {
   extern __shared__ __align__(16) float stage_s[];   // kDeltaStages buffers of [q: 8 R | k: 8 R | g: 8 R | v: 16 | beta | 3 unused]
   constexpr int kPadded = kDeltaLanes * R;
   constexpr int kRow = 3 * kPadded + kDeltaColumns + 4;
@@ -194,6 +196,28 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* 
       const int row = block_of_rows * kDeltaBlock + n;
       if (row >= count) break;
       const float* cur = stage_s + (row % kDeltaStages) * kRow;
+      if (PLAIN) {
+        const float u = cur[3 * kPadded + kDeltaColumns] * cur[3 * kPadded + (tid / kDeltaLanes)];   // beta v
+        float read2[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int j = 0; j < R / 4; ++j) {
+          const float4 q4 = *reinterpret_cast<const float4*>(cur + j * 4 * kDeltaLanes + lane * 4);
+          const float4 k4 = *reinterpret_cast<const float4*>(cur + kPadded + j * 4 * kDeltaLanes + lane * 4);
+          const float4 g4 = *reinterpret_cast<const float4*>(cur + 2 * kPadded + j * 4 * kDeltaLanes + lane * 4);
+          const float q[4] = {q4.x, q4.y, q4.z, q4.w}, k[4] = {k4.x, k4.y, k4.z, k4.w}, g[4] = {g4.x, g4.y, g4.z, g4.w};
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int i = 4 * j + c;
+            S[i] = S[i] * g[c] + k[c] * u;
+            read2[c & 1] += q[c] * S[i];
+          }
+        }
+        float read = read2[0] + read2[1];
+#pragma unroll
+        for (int offset = kDeltaLanes / 2; offset > 0; offset >>= 1) read += __shfl_xor_sync(0xffffffffu, read, offset);
+        if (live && lane == 0) out[(size_t)(first + row) * heads * vdim + head * vdim + column] = read;
+        continue;
+      }
       // k . (g S)_j, q . (g S)_j, q . k (this lane's share), each in two chains of sums
       float reach2[2] = {0.0f, 0.0f}, read2[2] = {0.0f, 0.0f}, both2[2] = {0.0f, 0.0f};
       float kk[R];
@@ -221,7 +245,7 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* 
         both += __shfl_xor_sync(0xffffffffu, both, offset);
       }
       const float v = cur[3 * kPadded + (tid / kDeltaLanes)], beta = cur[3 * kPadded + kDeltaColumns];
-      const float u = beta * (v - correct * reach);   // correct: 1 for the delta rule, 0 for the plain write u = beta v
+      const float u = beta * (v - reach);
 #pragma unroll
       for (int i = 0; i < R; ++i) S[i] += kk[i] * u;
       if (live && lane == 0) out[(size_t)(first + row) * heads * vdim + head * vdim + column] = read + both * u;
@@ -338,13 +362,13 @@ __global__ void __launch_bounds__(256) ssd_finish_kernel(const float* __restrict
   }
 }
 
-template <int R>
+template <int R, bool PLAIN>
 static int launch_delta_rule(const float* prep, float* state, long long state_stride, const int* seq_starts, const int* state_slots, float* out, int entries,
-                             int heads, int kv_heads, int dim, int vdim, float correct, cudaStream_t stream) {
+                             int heads, int kv_heads, int dim, int vdim, cudaStream_t stream) {
   const int column_blocks = (vdim + kDeltaColumns - 1) / kDeltaColumns;
   const size_t smem = kDeltaStages * (size_t)(3 * kDeltaLanes * R + kDeltaColumns + 4) * sizeof(float);
-  delta_rule_kernel<R><<<dim3(heads * column_blocks, entries), kDeltaThreads, smem, stream>>>(prep, state, state_stride, seq_starts, state_slots, out, heads, kv_heads,
-                                                                                           dim, vdim, correct);
+  delta_rule_kernel<R, PLAIN><<<dim3(heads * column_blocks, entries), kDeltaThreads, smem, stream>>>(prep, state, state_stride, seq_starts, state_slots, out, heads,
+                                                                                                  kv_heads, dim, vdim);
   return (int)cudaGetLastError();
 }
 
@@ -386,7 +410,9 @@ TLIE_EXPORT int tlie_delta_rule(const float* prep, float* state, long long state
   if (dim < 1 || dim > 256 || kv_heads < 1 || heads % kv_heads != 0) return (int)cudaErrorInvalidValue;
   const int r = 4 * ((dim + 4 * kDeltaLanes - 1) / (4 * kDeltaLanes));
 #define TLIE_DELTA(R) \
-  if (r <= R) return launch_delta_rule<R>(prep, state, state_stride, seq_starts, state_slots, out, entries, heads, kv_heads, dim, vdim, plain ? 0.0f : 1.0f, stream)
+  if (r <= R)   \
+    return plain ? launch_delta_rule<R, true>(prep, state, state_stride, seq_starts, state_slots, out, entries, heads, kv_heads, dim, vdim, stream) \
+                 : launch_delta_rule<R, false>(prep, state, state_stride, seq_starts, state_slots, out, entries, heads, kv_heads, dim, vdim, stream)
   TLIE_DELTA(4);
   TLIE_DELTA(8);
   TLIE_DELTA(12);

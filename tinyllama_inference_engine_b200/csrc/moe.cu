@@ -3,10 +3,12 @@
 //   moe_route     per token: z = W_router x (32-bit), s = sigmoid(z), choice = s + correction.  Experts form ``groups`` equal groups
 //                 of neighbours; a group's score is the sum of its two largest choice scores; only experts of the ``keep`` best
 //                 groups can be chosen.  The ``top`` largest choice scores among them are chosen (ties: the lower index); their
-//                 weights are s / (sum of the chosen s + 1e-20) * route_scale.
+//                 weights are s / (sum of the chosen s + 1e-20) * route_scale (``normalize`` 0: s * route_scale, the scores as they are).
 //   moe_gate_up   per (token, chosen expert): act(W_gate x) * (W_up x), straight from the expert's rows (steps of few rows, and the
 //                 32-bit path): a warp per output, the sums in a fixed order.
 //   moe_down      per token: sum over its chosen experts of weight * W_down act, plus the shared branch if there is one.
+//                 ``weight_input``: the weight multiplies what the expert reads instead (moe_gate_up scales the token as it loads it,
+//                 moe_down adds the experts' outputs as they are).
 //
 // Expert weights are stacked: gate_up [experts][2 ff][width] (gate rows, then up rows), down [experts][width][ff].
 // Activation codes: 0 silu, 1 gelu in its tanh form.

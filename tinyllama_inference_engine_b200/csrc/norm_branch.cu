@@ -4,7 +4,7 @@
 //   out[r]       = norm(residual[rows[r]]) * next_weight   (if out is given; rows null: every row in order)
 //
 // in one kernel, a CTA per row.  ``centred`` 1: (x - mean) / sqrt(mean((x - mean)^2) + eps), the layer norm without a bias;
-// 0: x / sqrt(mean(x^2) + eps).  The row waits in shared memory as 32-bit numbers between the passes; mean, variance (of
+// 0: x / sqrt(mean(x^2) + eps).  ``groups`` > 1: the statistics are taken over each of that many equal consecutive parts of the row.  The row waits in shared memory as 32-bit numbers between the passes; mean, variance (of
 // the deviations, after the mean is known), the sum into the stream and the second norm are 32-bit whatever y and out are
 // stored as.  The order of a row's sums depends on the block size alone.
 //
