@@ -191,33 +191,50 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* 
     delta_wait<kBlocksAhead - 1>();   // this thread's copies of this block's rows have landed ...
     __syncthreads();                  // ... and so have everyone's; and everyone is done with the block before, whose buffers are written next
     issue(block_of_rows + kBlocksAhead);
+    if (PLAIN) {
+      // the block's four rows: the state's chain first, every row leaving its share of the read-out; then the four sums across the column's
+      // lanes side by side, so that a round of shuffles is waited for once per block and not once per row
+      float reads[kDeltaBlock];
+#pragma unroll
+      for (int n = 0; n < kDeltaBlock; ++n) {
+        const int row = block_of_rows * kDeltaBlock + n;
+        reads[n] = 0.0f;
+        if (row < count) {
+          const float* cur = stage_s + (row % kDeltaStages) * kRow;
+          const float u = cur[3 * kPadded + kDeltaColumns] * cur[3 * kPadded + (tid / kDeltaLanes)];   // beta v
+          float read2[2] = {0.0f, 0.0f};
+#pragma unroll
+          for (int j = 0; j < R / 4; ++j) {
+            const float4 q4 = *reinterpret_cast<const float4*>(cur + j * 4 * kDeltaLanes + lane * 4);
+            const float4 k4 = *reinterpret_cast<const float4*>(cur + kPadded + j * 4 * kDeltaLanes + lane * 4);
+            const float4 g4 = *reinterpret_cast<const float4*>(cur + 2 * kPadded + j * 4 * kDeltaLanes + lane * 4);
+            const float q[4] = {q4.x, q4.y, q4.z, q4.w}, k[4] = {k4.x, k4.y, k4.z, k4.w}, g[4] = {g4.x, g4.y, g4.z, g4.w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const int i = 4 * j + c;
+              S[i] = S[i] * g[c] + k[c] * u;
+              read2[c & 1] += q[c] * S[i];
+            }
+          }
+          reads[n] = read2[0] + read2[1];
+        }
+      }
+#pragma unroll
+      for (int offset = kDeltaLanes / 2; offset > 0; offset >>= 1)
+#pragma unroll
+        for (int n = 0; n < kDeltaBlock; ++n) reads[n] += __shfl_xor_sync(0xffffffffu, reads[n], offset);
+#pragma unroll
+      for (int n = 0; n < kDeltaBlock; ++n) {
+        const int row = block_of_rows * kDeltaBlock + n;
+        if (row < count && live && lane == 0) out[(size_t)(first + row) * heads * vdim + head * vdim + column] = reads[n];
+      }
+      continue;
+    }
 #pragma unroll
     for (int n = 0; n < kDeltaBlock; ++n) {
       const int row = block_of_rows * kDeltaBlock + n;
       if (row >= count) break;
       const float* cur = stage_s + (row % kDeltaStages) * kRow;
-      if (PLAIN) {
-        const float u = cur[3 * kPadded + kDeltaColumns] * cur[3 * kPadded + (tid / kDeltaLanes)];   // beta v
-        float read2[2] = {0.0f, 0.0f};
-#pragma unroll
-        for (int j = 0; j < R / 4; ++j) {
-          const float4 q4 = *reinterpret_cast<const float4*>(cur + j * 4 * kDeltaLanes + lane * 4);
-          const float4 k4 = *reinterpret_cast<const float4*>(cur + kPadded + j * 4 * kDeltaLanes + lane * 4);
-          const float4 g4 = *reinterpret_cast<const float4*>(cur + 2 * kPadded + j * 4 * kDeltaLanes + lane * 4);
-          const float q[4] = {q4.x, q4.y, q4.z, q4.w}, k[4] = {k4.x, k4.y, k4.z, k4.w}, g[4] = {g4.x, g4.y, g4.z, g4.w};
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const int i = 4 * j + c;
-            S[i] = S[i] * g[c] + k[c] * u;
-            read2[c & 1] += q[c] * S[i];
-          }
-        }
-        float read = read2[0] + read2[1];
-#pragma unroll
-        for (int offset = kDeltaLanes / 2; offset > 0; offset >>= 1) read += __shfl_xor_sync(0xffffffffu, read, offset);
-        if (live && lane == 0) out[(size_t)(first + row) * heads * vdim + head * vdim + column] = read;
-        continue;
-      }
       // k . (g S)_j, q . (g S)_j, q . k (this lane's share), each in two chains of sums
       float reach2[2] = {0.0f, 0.0f}, read2[2] = {0.0f, 0.0f}, both2[2] = {0.0f, 0.0f};
       float kk[R];
