@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(const T* __restrict_
                                                             const float* __restrict__ a_log, const float* __restrict__ dt_bias, const float* __restrict__ state,
                                                             long long state_stride, long long conv_offset, const int* __restrict__ token_seq,
                                                             const int* __restrict__ seq_starts, const int* __restrict__ state_slots, float* __restrict__ prep,
-                                                            int heads, int kv_heads, int dim, int vdim, int taps, float unit_eps, float q_scale) {
+                                                            int heads, int kv_heads, int dim, int vdim, int taps, float unit_eps, float q_scale, int keep) {
   __shared__ float conv_s[256];   // the convolved and activated channels of a q or k head (dim <= 256)
   __shared__ float scratch[32];
   const int t = blockIdx.x, part = blockIdx.y;
@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(const T* __restrict_
   const int r = t - first;
   const int qk = kv_heads * dim;
   const int channels = 2 * qk + heads * vdim;
-  const float* conv_state = state + (size_t)state_slots[entry] * state_stride + conv_offset;
+  float* conv_state = const_cast<float*>(state) + (size_t)state_slots[entry] * state_stride + conv_offset;
   const int width = channels + heads + heads * dim;
   float* out = prep + (size_t)t * width;
   const bool unit = part < 2 * kv_heads;
@@ -73,6 +73,7 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(const T* __restrict_
       const int back = r - (taps - 1) + j;   // row of the entry this tap reads; negative: before this step
       const float x = back >= 0 ? to_float(rows[(size_t)(first + back) * row_stride + c]) : conv_state[(size_t)(taps - 1 + back) * channels + c];
       sum += taps_w[c * taps + j] * x;
+      if (keep && j > 0) conv_state[(size_t)(j - 1) * channels + c] = x;   // a step of single rows: this thread alone reads and renews its channel's inputs
     }
     const float y = sum * sigmoid_f(sum);
     if (unit) {
@@ -191,7 +192,7 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* 
     delta_wait<kBlocksAhead - 1>();   // this thread's copies of this block's rows have landed ...
     __syncthreads();                  // ... and so have everyone's; and everyone is done with the block before, whose buffers are written next
     issue(block_of_rows + kBlocksAhead);
-    if (PLAIN) {
+    if constexpr (PLAIN) {
       // the block's four rows: the state's chain first, every row leaving its share of the read-out; then the four sums across the column's
       // lanes side by side, so that a round of shuffles is waited for once per block and not once per row
       float reads[kDeltaBlock];
@@ -228,8 +229,7 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* 
         const int row = block_of_rows * kDeltaBlock + n;
         if (row < count && live && lane == 0) out[(size_t)(first + row) * heads * vdim + head * vdim + column] = reads[n];
       }
-      continue;
-    }
+    } else {
 #pragma unroll
     for (int n = 0; n < kDeltaBlock; ++n) {
       const int row = block_of_rows * kDeltaBlock + n;
@@ -267,6 +267,7 @@ __global__ void __launch_bounds__(kDeltaThreads) delta_rule_kernel(const float* 
       for (int i = 0; i < R; ++i) S[i] += kk[i] * u;
       if (live && lane == 0) out[(size_t)(first + row) * heads * vdim + head * vdim + column] = read + both * u;
     }
+    }
   }
   delta_wait<0>();
   if (live && count > 0) {
@@ -298,7 +299,7 @@ __global__ void delta_gate_norm_kernel(const float* __restrict__ o, const T* __r
 }
 
 // prep rows of the same layout for a recurrence whose forget gate also writes: rows = [q: H dim | f: H dim | v: H vdim] (products),
-// q = silu(q); f = lower + (1 - lower) sigmoid(f + f_bias) is the decay, 1 - f the key; beta = 1.  One CTA per token.
+// q = silu(q); f = lower + (1 - lower) sigmoid(f + f_bias) is the decay, 1 - f the key; beta = 1.  A thread per number, so that a step of few rows still fills SMs.
 template <typename T>
 __global__ void __launch_bounds__(256) hgrn2_prepare_kernel(const T* __restrict__ rows, int row_stride, const float* __restrict__ f_bias, const float* __restrict__ lower,
                                                             float* __restrict__ prep, int heads, int dim, int vdim) {
@@ -306,53 +307,70 @@ __global__ void __launch_bounds__(256) hgrn2_prepare_kernel(const T* __restrict_
   const T* row = rows + (size_t)t * row_stride;
   const int qk = heads * dim, values = heads * vdim;
   float* out = prep + (size_t)t * (3 * qk + values + heads);
-  for (int i = threadIdx.x; i < qk; i += blockDim.x) {
-    const float q = to_float(row[i]);
-    const float low = lower[i];
-    const float f = low + (1.0f - low) * sigmoid_f(to_float(row[qk + i]) + (f_bias != nullptr ? f_bias[i] : 0.0f));
-    out[i] = q * sigmoid_f(q);
-    out[qk + i] = 1.0f - f;
-    out[2 * qk + values + heads + i] = f;
+  const int w = blockIdx.y * blockDim.x + threadIdx.x;   // one piece of work a thread: a (q, f) channel, a value or a head's beta
+  if (w < qk) {
+    const float q = to_float(row[w]);
+    const float low = lower[w];
+    const float f = low + (1.0f - low) * sigmoid_f(to_float(row[qk + w]) + (f_bias != nullptr ? f_bias[w] : 0.0f));
+    out[w] = q * sigmoid_f(q);
+    out[qk + w] = 1.0f - f;
+    out[2 * qk + values + heads + w] = f;
+  } else if (w < qk + values) {
+    out[2 * qk + (w - qk)] = to_float(row[2 * qk + (w - qk)]);
+  } else if (w < qk + values + heads) {
+    out[2 * qk + values + (w - qk - values)] = 1.0f;
   }
-  for (int i = threadIdx.x; i < values; i += blockDim.x) out[2 * qk + i] = to_float(row[2 * qk + i]);
-  for (int i = threadIdx.x; i < heads; i += blockDim.x) out[2 * qk + values + i] = 1.0f;
 }
 
 // prep rows of the same layout for a state-space layer: rows = [z: inner | x: inner | B: G N | C: G N | dt: H] (products, inner = H vdim).
 // x, B and C pass a causal convolution over time per channel (taps [channels, n] with a bias, the last column the current token's;
 // inputs before an entry's first row come from the request's state at ``conv_offset``) and silu; dt = softplus(dt + dt_bias); the
-// query is C, the key B, the value x, beta = dt and the decay exp(-exp(A_log_h) dt) for all N channels of head h.  One CTA per token.
+// query is C, the key B, the value x, beta = dt and the decay exp(-exp(A_log_h) dt) for all N channels of head h.  A thread per number.
 template <typename T>
 __global__ void __launch_bounds__(256) ssd_prepare_kernel(const T* __restrict__ rows, int row_stride, const float* __restrict__ taps_w, const float* __restrict__ conv_bias,
                                                           const float* __restrict__ a_log, const float* __restrict__ dt_bias, const float* __restrict__ state,
                                                           long long state_stride, long long conv_offset, const int* __restrict__ token_seq,
                                                           const int* __restrict__ seq_starts, const int* __restrict__ state_slots, float* __restrict__ prep, int heads,
-                                                          int groups, int n, int vdim, int taps) {
+                                                          int groups, int n, int vdim, int taps, int keep) {
   const int t = blockIdx.x;
   const int entry = token_seq[t];
   const int first = seq_starts[entry];
   const int r = t - first;
   const int inner = heads * vdim, gn = groups * n;
   const int channels = inner + 2 * gn;
-  const float* conv_state = state + (size_t)state_slots[entry] * state_stride + conv_offset;
+  float* conv_state = const_cast<float*>(state) + (size_t)state_slots[entry] * state_stride + conv_offset;
   float* out = prep + (size_t)t * (2 * gn + inner + heads + heads * n);
-  for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+  const int w = blockIdx.y * blockDim.x + threadIdx.x;   // one piece of work a thread: a channel of the convolution, or one key channel's decay of a head
+  // the step sizes and decays of the heads whose channels this CTA writes: once per head, not once per channel
+  __shared__ float dt_s[258], decay_s[258];
+  const int lo = max((int)(blockIdx.y * blockDim.x), channels), hi = min((int)((blockIdx.y + 1) * blockDim.x), channels + heads * n);
+  const int h0 = lo < hi ? (lo - channels) / n : 0;
+  if (lo < hi) {
+    const int h1 = (hi - 1 - channels) / n;
+    for (int j = threadIdx.x; j <= h1 - h0; j += blockDim.x) {
+      const float dt = softplus_f(to_float(rows[(size_t)t * row_stride + 2 * inner + 2 * gn + h0 + j]) + dt_bias[h0 + j]);
+      dt_s[j] = dt;
+      decay_s[j] = expf(-expf(a_log[h0 + j]) * dt);
+    }
+  }
+  __syncthreads();
+  if (w < channels) {
+    const int c = w;
     float sum = conv_bias != nullptr ? conv_bias[c] : 0.0f;
     for (int j = 0; j < taps; ++j) {
       const int back = r - (taps - 1) + j;
       const float x = back >= 0 ? to_float(rows[(size_t)(first + back) * row_stride + inner + c]) : conv_state[(size_t)(taps - 1 + back) * channels + c];
       sum += taps_w[c * taps + j] * x;
+      if (keep && j > 0) conv_state[(size_t)(j - 1) * channels + c] = x;   // a step of single rows: this thread alone reads and renews its channel's inputs
     }
     const float y = sum * sigmoid_f(sum);
     // x -> the values; B -> the keys; C -> the queries
     const int at = c < inner ? 2 * gn + c : (c < inner + gn ? gn + (c - inner) : c - inner - gn);
     out[at] = y;
-  }
-  for (int h = threadIdx.x; h < heads; h += blockDim.x) {
-    const float dt = softplus_f(to_float(rows[(size_t)t * row_stride + 2 * inner + 2 * gn + h]) + dt_bias[h]);
-    out[2 * gn + inner + h] = dt;
-    const float decay = expf(-expf(a_log[h]) * dt);
-    for (int i = 0; i < n; ++i) out[2 * gn + inner + heads + h * n + i] = decay;
+  } else if (w < channels + heads * n) {
+    const int h = (w - channels) / n, i = (w - channels) - h * n;
+    if (i == 0) out[2 * gn + inner + h] = dt_s[h - h0];
+    out[2 * gn + inner + heads + h * n + i] = decay_s[h - h0];
   }
 }
 
@@ -397,21 +415,22 @@ TLIE_EXPORT int tlie_delta_prepare(int dtype, const void* rows, int row_stride, 
                                    const float* taps_w, const float* a_log,
                                    const float* dt_bias, float* state, long long state_stride, long long conv_offset, const int* token_seq, const int* seq_starts,
                                    const int* state_slots, float* prep, int tokens, int entries, int heads, int kv_heads, int dim, int vdim, int taps, float unit_eps,
-                                   float q_scale, cudaStream_t stream) {
+                                   float q_scale, int single_rows, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (taps < 1 || taps > kDeltaMaxTaps || kv_heads < 1 || heads % kv_heads != 0 || 2 * kv_heads + heads > 65535) return (int)cudaErrorInvalidValue;
   const int channels = 2 * kv_heads * dim + heads * vdim;
   if (dim > 256) return (int)cudaErrorInvalidValue;
   const dim3 parts(tokens, 2 * kv_heads + heads);
+  const int keep = (single_rows && tokens == entries && taps > 1) ? 1 : 0;   // every entry brings one row: the kernel renews the kept inputs itself
   if (dtype == TLIE_F32)
     delta_prepare_kernel<float><<<parts, 128, 0, stream>>>((const float*)rows, row_stride, beta_offset, (const float*)a, a_stride, decay_per_head, taps_w, a_log, dt_bias, state, state_stride,
-                                                           conv_offset, token_seq, seq_starts, state_slots, prep, heads, kv_heads, dim, vdim, taps, unit_eps, q_scale);
+                                                           conv_offset, token_seq, seq_starts, state_slots, prep, heads, kv_heads, dim, vdim, taps, unit_eps, q_scale, keep);
   else
     delta_prepare_kernel<__nv_bfloat16><<<parts, 128, 0, stream>>>((const __nv_bfloat16*)rows, row_stride, beta_offset, (const __nv_bfloat16*)a, a_stride, decay_per_head, taps_w, a_log, dt_bias,
                                                                    state, state_stride, conv_offset, token_seq, seq_starts, state_slots, prep, heads, kv_heads, dim,
-                                                                   vdim, taps, unit_eps, q_scale);
+                                                                   vdim, taps, unit_eps, q_scale, keep);
   cudaError_t status = cudaGetLastError();
-  if (status != cudaSuccess || taps == 1) return (int)status;
+  if (status != cudaSuccess || taps == 1 || keep) return (int)status;
   const dim3 grid((channels + 127) / 128, entries);
   if (dtype == TLIE_F32)
     delta_conv_state_kernel<float><<<grid, 128, 0, stream>>>((const float*)rows, row_stride, state, state_stride, conv_offset, seq_starts, state_slots, channels, taps);
@@ -456,28 +475,31 @@ TLIE_EXPORT int tlie_delta_gate_norm(int dtype, const float* o, const void* gate
 TLIE_EXPORT int tlie_hgrn2_prepare(int dtype, const void* rows, int row_stride, const float* f_bias, const float* lower, float* prep, int tokens, int heads, int dim,
                                    int vdim, cudaStream_t stream) {
   if (tokens <= 0) return 0;
+  const dim3 grid(tokens, (heads * dim + heads * vdim + heads + 255) / 256);
   if (dtype == TLIE_F32)
-    hgrn2_prepare_kernel<float><<<tokens, 256, 0, stream>>>((const float*)rows, row_stride, f_bias, lower, prep, heads, dim, vdim);
+    hgrn2_prepare_kernel<float><<<grid, 256, 0, stream>>>((const float*)rows, row_stride, f_bias, lower, prep, heads, dim, vdim);
   else
-    hgrn2_prepare_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)rows, row_stride, f_bias, lower, prep, heads, dim, vdim);
+    hgrn2_prepare_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)rows, row_stride, f_bias, lower, prep, heads, dim, vdim);
   return (int)cudaGetLastError();
 }
 
 // The convolution's inputs (columns [inner, inner + channels) of ``rows``) are moved on in the request's state afterwards.
 TLIE_EXPORT int tlie_ssd_prepare(int dtype, const void* rows, int row_stride, const float* taps_w, const float* conv_bias, const float* a_log, const float* dt_bias,
                                  float* state, long long state_stride, long long conv_offset, const int* token_seq, const int* seq_starts, const int* state_slots,
-                                 float* prep, int tokens, int entries, int heads, int groups, int n, int vdim, int taps, cudaStream_t stream) {
+                                 float* prep, int tokens, int entries, int heads, int groups, int n, int vdim, int taps, int single_rows, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (taps < 1 || taps > kDeltaMaxTaps || groups < 1 || heads % groups != 0) return (int)cudaErrorInvalidValue;
   const int inner = heads * vdim, channels = inner + 2 * groups * n;
+  const int keep = (single_rows && tokens == entries && taps > 1) ? 1 : 0;
+  const dim3 work(tokens, (channels + heads * n + 255) / 256);
   if (dtype == TLIE_F32)
-    ssd_prepare_kernel<float><<<tokens, 256, 0, stream>>>((const float*)rows, row_stride, taps_w, conv_bias, a_log, dt_bias, state, state_stride, conv_offset, token_seq,
-                                                          seq_starts, state_slots, prep, heads, groups, n, vdim, taps);
+    ssd_prepare_kernel<float><<<work, 256, 0, stream>>>((const float*)rows, row_stride, taps_w, conv_bias, a_log, dt_bias, state, state_stride, conv_offset, token_seq,
+                                                          seq_starts, state_slots, prep, heads, groups, n, vdim, taps, keep);
   else
-    ssd_prepare_kernel<__nv_bfloat16><<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)rows, row_stride, taps_w, conv_bias, a_log, dt_bias, state, state_stride,
-                                                                  conv_offset, token_seq, seq_starts, state_slots, prep, heads, groups, n, vdim, taps);
+    ssd_prepare_kernel<__nv_bfloat16><<<work, 256, 0, stream>>>((const __nv_bfloat16*)rows, row_stride, taps_w, conv_bias, a_log, dt_bias, state, state_stride,
+                                                                  conv_offset, token_seq, seq_starts, state_slots, prep, heads, groups, n, vdim, taps, keep);
   cudaError_t status = cudaGetLastError();
-  if (status != cudaSuccess || taps == 1) return (int)status;
+  if (status != cudaSuccess || taps == 1 || keep) return (int)status;
   const dim3 grid((channels + 127) / 128, entries);
   if (dtype == TLIE_F32)
     delta_conv_state_kernel<float><<<grid, 128, 0, stream>>>((const float*)rows + inner, row_stride, state, state_stride, conv_offset, seq_starts, state_slots, channels, taps);

@@ -23,7 +23,7 @@ __global__ void __launch_bounds__(256) pair_embedding_kernel(const T* __restrict
                                                              const int* __restrict__ state_slots, const float* __restrict__ state, long long state_stride,
                                                              long long state_offset, const float* __restrict__ weight, float eps, float scale, float* __restrict__ residual,
                                                              int width, int vocab, int buckets, long long mul_prev, long long mul_cur, int groups,
-                                                             int* __restrict__ error_flag) {
+                                                             int* __restrict__ error_flag, float* __restrict__ renew) {
   extern __shared__ float row_s[];
   __shared__ float scratch[32];
   __shared__ float invs[kFilterMaxGroups];
@@ -47,6 +47,8 @@ __global__ void __launch_bounds__(256) pair_embedding_kernel(const T* __restrict
   const T* token_row = table + (size_t)id * width;
   for (int i = threadIdx.x; i < width; i += blockDim.x) row_s[i] = to_float(token_row[i]) * scale + (pair_row != nullptr ? to_float(pair_row[i]) : 0.0f);
   __syncthreads();
+  // a step of single rows: this CTA is the only one that touches its request's word, and every thread has read it by now
+  if (renew != nullptr && threadIdx.x == 0) renew[(size_t)state_slots[token_seq[t]] * state_stride + state_offset] = __int_as_float(ids[t]);
   float* out = residual + (size_t)t * width;
   if (weight == nullptr) {
     for (int i = threadIdx.x; i < width; i += blockDim.x) out[i] = row_s[i];
@@ -75,19 +77,22 @@ __global__ void last_token_kernel(const int* __restrict__ ids, const int* __rest
 template <typename T>
 __global__ void __launch_bounds__(256) conv_residual_kernel(const T* __restrict__ x, const float* __restrict__ taps_w, const float* __restrict__ state, long long state_stride,
                                                             long long state_offset, const int* __restrict__ token_seq, const int* __restrict__ seq_starts,
-                                                            const int* __restrict__ state_slots, T* __restrict__ out, int channels, int taps) {
+                                                            const int* __restrict__ state_slots, T* __restrict__ out, int channels, int taps, int keep) {
   const int t = blockIdx.x;
   const int entry = token_seq[t];
   const int first = seq_starts[entry];
   const int r = t - first;
-  const float* kept = state + (size_t)state_slots[entry] * state_stride + state_offset;
+  float* kept = const_cast<float*>(state) + (size_t)state_slots[entry] * state_stride + state_offset;
   for (int c = threadIdx.x; c < channels; c += blockDim.x) {
     const float now = to_float(x[(size_t)t * channels + c]);
     float sum = taps_w[c * taps + taps - 1] * now;
     for (int j = 0; j < taps - 1; ++j) {
       const int back = r - (taps - 1) + j;
-      sum += taps_w[c * taps + j] * (back >= 0 ? to_float(x[(size_t)(first + back) * channels + c]) : kept[(size_t)(taps - 1 + back) * channels + c]);
+      const float past = back >= 0 ? to_float(x[(size_t)(first + back) * channels + c]) : kept[(size_t)(taps - 1 + back) * channels + c];
+      sum += taps_w[c * taps + j] * past;
+      if (keep && j > 0) kept[(size_t)(j - 1) * channels + c] = past;   // a step of single rows: this thread alone reads and renews its channel's inputs
     }
+    if (keep && taps > 1) kept[(size_t)(taps - 2) * channels + c] = now;
     out[(size_t)t * channels + c] = from_float<T>(now + sum);
   }
 }
@@ -122,7 +127,7 @@ __device__ __forceinline__ void filter_store8(__nv_bfloat16* dst, const float (&
 template <typename T>
 __global__ void __launch_bounds__(256) conv_residual_wide_kernel(const T* __restrict__ x, const float* __restrict__ taps_w, const float* __restrict__ state, long long state_stride,
                                                                  long long state_offset, const int* __restrict__ token_seq, const int* __restrict__ seq_starts,
-                                                                 const int* __restrict__ state_slots, T* __restrict__ out, int channels, int taps, int rows) {
+                                                                 const int* __restrict__ state_slots, T* __restrict__ out, int channels, int taps, int rows, int keep) {
   const int per_row = channels / 8;
   const int index = blockIdx.x * blockDim.x + threadIdx.x;
   if (index >= rows * per_row) return;
@@ -130,7 +135,7 @@ __global__ void __launch_bounds__(256) conv_residual_wide_kernel(const T* __rest
   const int entry = token_seq[t];
   const int first = seq_starts[entry];
   const int r = t - first;
-  const float* kept = state + (size_t)state_slots[entry] * state_stride + state_offset;
+  float* kept = const_cast<float*>(state) + (size_t)state_slots[entry] * state_stride + state_offset;
   float now[8], sum[8], past[8];
   filter_load8(x + (size_t)t * channels + c0, now);
 #pragma unroll
@@ -145,6 +150,14 @@ __global__ void __launch_bounds__(256) conv_residual_wide_kernel(const T* __rest
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) sum[i] += taps_w[(c0 + i) * taps + j] * past[i];
+    if (keep && j > 0) {   // a step of single rows: this thread alone reads and renews its channels' inputs
+#pragma unroll
+      for (int i = 0; i < 8; ++i) kept[(size_t)(j - 1) * channels + c0 + i] = past[i];
+    }
+  }
+  if (keep && taps > 1) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) kept[(size_t)(taps - 2) * channels + c0 + i] = now[i];
   }
 #pragma unroll
   for (int i = 0; i < 8; ++i) now[i] += sum[i];
@@ -184,52 +197,56 @@ __global__ void add_bias_kernel(T* __restrict__ x, const float* __restrict__ bia
 
 using namespace tlie;
 
-// ``pairs`` null: no second table.  ``weight`` null: no norm.  The state word at ``state_offset`` of a request's slot holds the bits of
+// ``pairs`` null: no second table.  ``weight`` null: no norm.  ``single_rows`` 1: every entry of the step brings exactly one row.  The state word at ``state_offset`` of a request's slot holds the bits of
 // the request's last token id (a new request's is never read: its first position is 0).
 TLIE_EXPORT int tlie_pair_embedding(int dtype, const void* table, const void* pairs, const int* ids, const int* positions, const int* token_seq, const int* seq_starts,
                                     const int* state_slots, float* state, long long state_stride, long long state_offset, const float* weight, float eps, float scale,
                                     float* residual, int rows, int entries, int width, int vocab, int buckets, long long mul_prev, long long mul_cur, int groups,
-                                    int* error_flag, cudaStream_t stream) {
+                                    int single_rows, int* error_flag, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (groups < 1 || groups > kFilterMaxGroups || width % groups != 0 || (pairs != nullptr && (buckets < 1 || state == nullptr)) || (size_t)width * sizeof(float) > 48 * 1024)
     return (int)cudaErrorInvalidValue;
   const size_t smem = (size_t)width * sizeof(float);
+  float* renew = (single_rows && pairs != nullptr && rows == entries) ? state : nullptr;   // every entry brings one row: no second launch
   if (dtype == TLIE_F32)
     pair_embedding_kernel<float><<<rows, 256, smem, stream>>>((const float*)table, (const float*)pairs, ids, positions, token_seq, seq_starts, state_slots, state, state_stride,
-                                                              state_offset, weight, eps, scale, residual, width, vocab, buckets, mul_prev, mul_cur, groups, error_flag);
+                                                              state_offset, weight, eps, scale, residual, width, vocab, buckets, mul_prev, mul_cur, groups, error_flag, renew);
   else
     pair_embedding_kernel<__nv_bfloat16><<<rows, 256, smem, stream>>>((const __nv_bfloat16*)table, (const __nv_bfloat16*)pairs, ids, positions, token_seq, seq_starts,
                                                                       state_slots, state, state_stride, state_offset, weight, eps, scale, residual, width, vocab, buckets,
-                                                                      mul_prev, mul_cur, groups, error_flag);
+                                                                      mul_prev, mul_cur, groups, error_flag, renew);
   cudaError_t status = cudaGetLastError();
-  if (status != cudaSuccess || pairs == nullptr) return (int)status;
+  if (status != cudaSuccess || pairs == nullptr || renew != nullptr) return (int)status;
   last_token_kernel<<<(entries + 127) / 128, 128, 0, stream>>>(ids, seq_starts, state_slots, state, state_stride, state_offset, entries);
   return (int)cudaGetLastError();
 }
 
+// ``single_rows`` 1: every entry of the step brings exactly one row; the kernel then renews the kept inputs itself and there is no second launch.
 TLIE_EXPORT int tlie_conv_residual(int dtype, const void* x, const float* taps_w, float* state, long long state_stride, long long state_offset, const int* token_seq,
-                                   const int* seq_starts, const int* state_slots, void* out, int rows, int entries, int channels, int taps, cudaStream_t stream) {
+                                   const int* seq_starts, const int* state_slots, void* out, int rows, int entries, int channels, int taps, int single_rows,
+                                   cudaStream_t stream) {
   if (rows <= 0) return 0;
+  const int keep = (single_rows && rows == entries && taps > 1) ? 1 : 0;
   if (taps < 1 || taps > kFilterMaxTaps || (taps > 1 && state == nullptr)) return (int)cudaErrorInvalidValue;
   const bool wide = channels % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;   // which kernel runs depends on the sizes alone
   const int wide_blocks = (int)(((long long)rows * (channels / 8) + 255) / 256);
   if (dtype == TLIE_F32) {
     if (wide)
       conv_residual_wide_kernel<float><<<wide_blocks, 256, 0, stream>>>((const float*)x, taps_w, state, state_stride, state_offset, token_seq, seq_starts, state_slots,
-                                                                        (float*)out, channels, taps, rows);
+                                                                        (float*)out, channels, taps, rows, keep);
     else
       conv_residual_kernel<float><<<rows, 256, 0, stream>>>((const float*)x, taps_w, state, state_stride, state_offset, token_seq, seq_starts, state_slots, (float*)out,
-                                                            channels, taps);
+                                                            channels, taps, keep);
   } else {
     if (wide)
       conv_residual_wide_kernel<__nv_bfloat16><<<wide_blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, taps_w, state, state_stride, state_offset, token_seq, seq_starts,
-                                                                                state_slots, (__nv_bfloat16*)out, channels, taps, rows);
+                                                                                state_slots, (__nv_bfloat16*)out, channels, taps, rows, keep);
     else
       conv_residual_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>((const __nv_bfloat16*)x, taps_w, state, state_stride, state_offset, token_seq, seq_starts, state_slots,
-                                                                    (__nv_bfloat16*)out, channels, taps);
+                                                                    (__nv_bfloat16*)out, channels, taps, keep);
   }
   cudaError_t status = cudaGetLastError();
-  if (status != cudaSuccess || taps == 1) return (int)status;
+  if (status != cudaSuccess || taps == 1 || keep) return (int)status;
   const dim3 grid((channels + 127) / 128, entries);
   if (dtype == TLIE_F32)
     conv_inputs_keep_kernel<float><<<grid, 128, 0, stream>>>((const float*)x, state, state_stride, state_offset, seq_starts, state_slots, channels, taps);

@@ -24,7 +24,7 @@ def _attention(width: int, sizes: dict) -> PartSpec:
     return PartSpec("mixed_heads_attention", {
         "hidden_size": width, "num_heads": sizes["heads"], "num_kv_heads": sizes["kv_heads"], "key_dim": sizes["dim"], "value_dim": sizes["vdim"],
         "scale": sizes["scale"], "window": 0, "distance_slopes": None, "mix_heads": False, "output_gate": False, "biases": True,
-        "rot_dims": sizes["rot"]["dims"], "rot_base": sizes["rot"]["base"],
+        "rot_dims": sizes["rot"]["dims"], "rot_base": sizes["rot"]["base"], "out_buffer": "mixer_left",   # it runs beside another mixer
     })
 
 

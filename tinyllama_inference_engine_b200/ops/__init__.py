@@ -579,6 +579,11 @@ def delta_state_words(heads: int, dim: int, vdim: int, channels: int, taps: int)
     return matrices + (taps - 1) * channels, matrices
 
 
+def _single_rows(ctx) -> int:
+    """1 if every entry of the step brings exactly one row (a kernel that keeps a request's last inputs then renews them itself, without a second launch)."""
+    return 1 if getattr(ctx, "max_q_len", 0) == 1 else 0
+
+
 def _state_rows(state, what: str):
     """(pointer, words between two requests' slots) of a per-request state [slots, words] in 32-bit; it may be a run of columns of wider rows."""
     if state is None or state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or not state.is_cuda:
@@ -611,7 +616,8 @@ def delta_prepare(rows, beta_offset: int, decay_in, taps, a_log, dt_bias, state,
                                                    c_longlong(decay_in.stride(0)), c_int(1 if decay_per_head else 0), _ptr(taps), _ptr(a_log),
                                                    _ptr(dt_bias), state_ptr, state_stride, c_longlong(conv_offset), _i32(ctx.token_seq, "token_seq"),
                                                    _i32(ctx.seq_starts, "seq_starts"), _i32(ctx.state_slots, "state_slots"), _ptr(prep), c_int(tokens), c_int(ctx.num_seqs),
-                                                   c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(taps.shape[1]), c_float(unit_eps), c_float(q_scale), _stream()),
+                                                   c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(taps.shape[1]), c_float(unit_eps), c_float(q_scale),
+                                                   c_int(_single_rows(ctx)), _stream()),
            "delta_prepare")
 
 
@@ -674,7 +680,7 @@ def ssd_prepare(rows, taps, conv_bias, a_log, dt_bias, state, conv_offset: int, 
     _check(delta_rule_library().tlie_ssd_prepare(_code(rows), c_void_p(rows.data_ptr()), c_int(rows.stride(0)), _ptr(taps), _ptr(conv_bias), _ptr(a_log), _ptr(dt_bias), state_ptr,
                                                  state_stride, c_longlong(conv_offset), _i32(ctx.token_seq, "token_seq"), _i32(ctx.seq_starts, "seq_starts"),
                                                  _i32(ctx.state_slots, "state_slots"), _ptr(prep), c_int(tokens), c_int(ctx.num_seqs), c_int(heads), c_int(groups), c_int(n),
-                                                 c_int(vdim), c_int(taps.shape[1]), _stream()), "ssd_prepare")
+                                                 c_int(vdim), c_int(taps.shape[1]), c_int(_single_rows(ctx)), _stream()), "ssd_prepare")
 
 
 def ssd_finish(read, prep, x_offset: int, rows, skip, weight, out, eps: float, heads: int, vdim: int, norm_groups: int) -> None:
@@ -710,7 +716,7 @@ def pair_embedding(table, pairs, ctx, state, state_offset: int, weight, eps: flo
                                                   _i32(ctx.token_seq, "token_seq"), _i32(ctx.seq_starts, "seq_starts"), _i32(ctx.state_slots, "state_slots"), state_ptr,
                                                   state_stride, c_longlong(state_offset), _ptr(weight), c_float(eps), c_float(scale), _ptr(residual), c_int(rows),
                                                   c_int(ctx.num_seqs), c_int(width), c_int(table.shape[0]), c_int(buckets), c_longlong(mul_prev), c_longlong(mul_cur),
-                                                  c_int(groups), _ptr(error_flag(residual.device)), _stream()), "pair_embedding")
+                                                  c_int(groups), c_int(_single_rows(ctx)), _ptr(error_flag(residual.device)), _stream()), "pair_embedding")
 
 
 def conv_residual(x, taps, state, state_offset: int, ctx, out) -> None:
@@ -722,7 +728,7 @@ def conv_residual(x, taps, state, state_offset: int, ctx, out) -> None:
     state_ptr, state_stride = (c_void_p(0), c_longlong(0)) if taps.shape[1] == 1 else _state_rows(state, "conv_residual")
     _check(sequence_library().tlie_conv_residual(_code(x), _ptr(x), _ptr(taps), state_ptr, state_stride, c_longlong(state_offset), _i32(ctx.token_seq, "token_seq"),
                                                  _i32(ctx.seq_starts, "seq_starts"), _i32(ctx.state_slots, "state_slots"), _ptr(out), c_int(rows), c_int(ctx.num_seqs),
-                                                 c_int(channels), c_int(taps.shape[1]), _stream()), "conv_residual")
+                                                 c_int(channels), c_int(taps.shape[1]), c_int(_single_rows(ctx)), _stream()), "conv_residual")
 
 
 def add_bias(x, bias) -> None:

@@ -101,7 +101,8 @@ class MixedHeadsAttention(Mixer):
     (one slope per head, or None for no bias), ``mix_heads`` (tensor ``<prefix>.talk`` [heads, heads], row h mixing into head h),
     ``output_gate`` (tensor ``<prefix>.g`` [heads * value_dim, hidden]); optional ``biases`` (q, k, v and the output projection have one each, the
     tensor's name with ``.b`` added, added in 32-bit) and ``rot_dims`` / ``rot_base`` (of every q and k head the first ``rot_dims`` columns turn, column i
-    with column i + rot_dims / 2, by position * rot_base^(-2i / rot_dims); keys are cached turned).
+    with column i + rot_dims / 2, by position * rot_base^(-2i / rot_dims); keys are cached turned); optional ``out_buffer`` (the workspace buffer
+    the output is written to, "mixer_out" unless given: a mixer that runs beside another one needs a buffer of its own).
     tensors: ``<prefix>.q`` [heads * key_dim, hidden], ``<prefix>.k`` [kv * key_dim, hidden], ``<prefix>.v`` [kv * value_dim, hidden],
     ``<prefix>.o`` [hidden, heads * value_dim].  q, k, v and the gate are one stacked product.  Keys and values are
     two planes of a page (of different widths if ``key_dim != value_dim``); scores, mix, softmax and the gate are 32-bit.
@@ -191,7 +192,7 @@ class MixedHeadsAttention(Mixer):
         if accumulate_into is not None:
             ops.linear_accumulate(mixed, self.w_o, accumulate_into, prepare)
             return None
-        out = ws.get("mixer_out", tokens, self.hidden, dtype)
+        out = ws.get(self.spec.get("out_buffer", "mixer_out"), tokens, self.hidden, dtype)
         ops.linear(mixed, self.w_o, out)
         if self.out_bias is not None:
             ops.add_bias(out, self.out_bias)

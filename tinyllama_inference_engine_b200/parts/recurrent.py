@@ -5,6 +5,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
+from ..errors import ConfigError
 from .base import CacheNeed, LayerCache, Mixer, register_part
 from .spec import PartSpec, TensorSpec
 
@@ -465,10 +466,10 @@ class ParallelMixers(Mixer):
     def forward(self, x, ctx, cache: LayerCache):
         ws, dtype = self.runtime.workspace, self.runtime.dtype
         left = self.left.forward(x, ctx, self._cache_of(0, cache))
-        kept = ws.get("mixer_left", left.shape[0], self.hidden, dtype)
-        ops.scaled_sum(left, left, 1.0, 0.0, kept)   # a copy: both mixers write the workspace's "mixer_out"
         right = self.right.forward(x, ctx, self._cache_of(1, cache))
-        ops.scaled_sum(kept, right, self.left_scale, self.right_scale, right)
+        if left.data_ptr() == right.data_ptr():
+            raise ConfigError(f"{self.prefix}: both mixers write one workspace buffer; give one of them an out_buffer of its own")
+        ops.scaled_sum(left, right, self.left_scale, self.right_scale, right)
         return right
 
 
