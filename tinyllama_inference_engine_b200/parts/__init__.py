@@ -1,4 +1,4 @@
-from . import attention, block, ends, filters, mlp, norm, position, recurrent, side  # noqa: F401  (registers the built-in parts)
+from . import attention, block, composite, ends, filters, mlp, norm, position, recurrent, side  # noqa: F401  (registers the built-in parts)
 from .base import (
     Block,
     CacheNeed,
