@@ -34,7 +34,7 @@ __device__ __forceinline__ void row_statistics(const float* row, int width, int 
 
 // The same per group: a row cut into ``groups`` equal consecutive parts, each with statistics of its own, left in shared memory
 // (``means`` and ``invs``, one entry per group) for all threads.  One group is the whole row, summed in the order it always was.
-constexpr int kNormMaxGroups = 64;
+constexpr int kNormMaxGroups = 256;
 __device__ __forceinline__ void group_statistics(const float* row, int width, int groups, int centred, float eps, float* scratch, float* means, float* invs) {
   const int part = width / groups;
   for (int g = 0; g < groups; ++g) {

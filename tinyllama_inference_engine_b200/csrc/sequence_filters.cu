@@ -15,7 +15,7 @@
 namespace tlie {
 
 constexpr int kFilterMaxTaps = 16;
-constexpr int kFilterMaxGroups = 64;
+constexpr int kFilterMaxGroups = 256;
 
 template <typename T>
 __global__ void __launch_bounds__(256) pair_embedding_kernel(const T* __restrict__ table, const T* __restrict__ pairs, const int* __restrict__ ids,

@@ -4,8 +4,8 @@ A decoder whose layers are listed one by one.  The embedding is a table row time
 the token and the one before it, under the model's norm.  The norm is an RMS norm over equal groups of a row.  A layer has such a
 norm before each sublayer and another on the sublayer's output, which joins the stream times a constant; what a sublayer reads
 first passes a short causal convolution over time that is added to its own input.  Three mixers: softmax attention (biased
-projections, a partial rotation, grouped heads) side by side with a state-space layer; a linear-attention layer whose forget gate
-also writes; the gated delta rule with one decay per head.  The feed-forward is a mixture of experts chosen by a sigmoid router
+projections, a partial rotation, grouped heads) added to a state-space layer's output on the same input; a linear-attention layer with one
+gate for forgetting and writing; the gated delta rule with one decay per head.  The feed-forward is a mixture of experts chosen by a sigmoid router
 whose scores multiply what the experts read, beside a shared expert.  The final norm, then a head of its own.
 Tensor names: ``embed``, ``bigram``, ``embed.norm``, ``final.norm``, ``head``, ``l<i>.norm1``, ``l<i>.norm1b``, ``l<i>.norm2``, ``l<i>.norm2b``,
 ``l<i>.canon1``, ``l<i>.canon2``, ``l<i>.mix.*``, ``l<i>.mlp.*``.  This file only names parts and sizes; every formula lives in the parts.

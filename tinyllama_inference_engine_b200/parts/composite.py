@@ -8,7 +8,7 @@ from .spec import PartSpec, TensorSpec
 
 
 class ParallelMixers(Mixer):
-    """Two mixers side by side that read the same input: out = left_scale * left(x) + right_scale * right(x).
+    """Two mixers run on one input, their outputs added with a constant each: out = left_scale * left(x) + right_scale * right(x).
 
     params: ``left``, ``right`` (PartSpecs of mixers; their tensors lie under ``<prefix>.left`` and ``<prefix>.right``), ``left_scale``, ``right_scale``.
     What the two keep between steps is one need: at most one of them may keep pages, and their per-request states lie one behind the
@@ -31,7 +31,7 @@ class ParallelMixers(Mixer):
         needs = [kind.cache_need(child) for _, child, kind in cls._children(spec)]
         paged = [need for need in needs if need.kind == "pages"]
         if len(paged) > 1:
-            raise ConfigError("mixers side by side: only one of them may keep pages")
+            raise ConfigError("two mixers on one input: only one of them may keep pages")
         pages = replace(paged[0], state_shape=()) if paged else CacheNeed()
         return pages.with_state(sum(need.state_words() for need in needs))   # the left mixer's words, then the right one's
 

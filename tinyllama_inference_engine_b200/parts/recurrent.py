@@ -276,7 +276,7 @@ class GatedDeltaRule(_MatrixRecurrence):
 
 
 class Hgrn2(_MatrixRecurrence):
-    """Linear attention whose forget gate also decides what is written.
+    """Linear attention with one gate for forgetting and writing: what a channel of the state gives up, it takes from the new value.
 
     q = silu(W_q x) (``heads`` of ``dim``), v = W_v x (``heads`` of ``vdim``), f = l + (1 - l) sigmoid(W_f x + b_f) per head and channel with the
     stored lower bound l in [0, 1).  Per head S <- diag(f) S + (1 - f) v^T, o = S^T q (no key, no other scale).  Each head's o is divided by
@@ -347,7 +347,7 @@ class StateSpaceDuality(_MatrixRecurrence):
 
     W_in x = [z: inner | x: inner | B: G N | C: G N | dt: heads] with inner = heads * vdim; x, B and C pass a causal convolution per channel
     (``<prefix>.conv`` [inner + 2 G N, taps] with the bias ``<prefix>.conv.b``, the last column the current token's, zeros before a request's start)
-    and silu; dt = softplus(dt + dt_bias), not clamped.  Per head h (group h // (heads / G)): S <- exp(-exp(A_log_h) dt) S + dt B x^T with S [N x vdim],
+    and silu; dt = softplus(dt + dt_bias) as it comes out, with no bounds put on it.  Per head h (group h // (heads / G)): S <- exp(-exp(A_log_h) dt) S + dt B x^T with S [N x vdim],
     y = S^T C + D_h x.  y (heads concatenated) times silu(z), then an RMS norm over each of ``norm_groups`` equal parts (``eps``), times
     ``<prefix>.norm`` [inner]; W_o.  State (32-bit, zero for a new request): the heads' matrices and the convolution's last taps - 1 inputs.
     Step sizes, decays, the recurrence, the gate and the norm are 32-bit.
