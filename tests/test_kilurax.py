@@ -338,6 +338,22 @@ def test_models_of_one_kind_of_layer(tmp_path, kind, dtype):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_widest_heads_and_longest_taps(tmp_path, dtype):
+    """Key widths and states of 200 and 256 channels (the recurrence's widest form, whose staged rows need more shared memory than a kernel gets unasked),
+    convolutions of seven taps, an attention head of 144."""
+    config = _config(72, 45, [_hgrn2(1, 200, 24, None), _delta(2, 1, 256, 16, 7, _moe(3, 1, 12)), _parallel(_left(2, 1, 144, 8, 0), _right(2, 16, 200, 1, 7, 1), None)],
+                     groups=2, taps=7)
+    folder = write_random_model(tmp_path / "wide", config, seed=4)
+    config, tensors = load_plain(folder)
+    requests = trace_tools.make_requests(45, [40, 9], seed=6)
+    full = {rid: _logits(config, tensors, tokens) for rid, tokens in requests.items()}
+    scale = max(float(v.abs().max()) for v in full.values())
+    for steps in (trace_tools.whole(requests), trace_tools.tail_decode(requests, tail=12), trace_tools.portions(requests)):
+        trace_tools.run_and_compare(_runner(folder, dtype), steps, full, atol=TOLERANCE[dtype] * scale, over_vocabulary=RMS[dtype], allowed_over=LOOSE_ROWS[dtype])
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("dtype,atol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("tokens,experts,top,width,ff,shared", [(5, 6, 2, 44, 10, True), (70, 8, 3, 64, 24, True), (300, 4, 1, 32, 16, False), (1, 3, 3, 24, 8, False),
                                                                 (700, 6, 3, 136, 200, True)])

@@ -402,6 +402,10 @@ static int launch_delta_rule(const float* prep, float* state, long long state_st
                              int heads, int kv_heads, int dim, int vdim, cudaStream_t stream) {
   const int column_blocks = (vdim + kDeltaColumns - 1) / kDeltaColumns;
   const size_t smem = kDeltaStages * (size_t)(3 * kDeltaLanes * R + kDeltaColumns + 4) * sizeof(float);
+  if (smem > 48 * 1024) {   // the widest heads' ring of staged rows is beyond what a kernel may ask for without saying so
+    cudaError_t e = cudaFuncSetAttribute(delta_rule_kernel<R, PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
   delta_rule_kernel<R, PLAIN><<<dim3(heads * column_blocks, entries), kDeltaThreads, smem, stream>>>(prep, state, state_stride, seq_starts, state_slots, out, heads,
                                                                                                   kv_heads, dim, vdim);
   return (int)cudaGetLastError();
